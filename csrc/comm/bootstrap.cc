@@ -1,0 +1,639 @@
+#include "msharp/bootstrap.h"
+
+#include <poll.h>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cerrno>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+
+namespace msharp {
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+constexpr uint32_t kMagic = 0x4d534850u;  // "MSHP"
+
+enum Op : uint32_t { kHello = 1, kBarrier, kAllgather, kBroadcast, kFdGather, kFdBroadcast, kAbort };
+
+struct Header {
+  uint32_t magic = kMagic;
+  uint32_t op = 0;
+  uint32_t seq = 0;
+  int32_t rank = 0;
+  uint64_t bytes = 0;
+};
+
+const char* op_name(uint32_t op) {
+  switch (op) {
+    case kHello:
+      return "hello";
+    case kBarrier:
+      return "barrier";
+    case kAllgather:
+      return "allgather";
+    case kBroadcast:
+      return "broadcast";
+    case kFdGather:
+      return "allgather_fd";
+    case kFdBroadcast:
+      return "broadcast_fd";
+    case kAbort:
+      return "abort";
+  }
+  return "unknown";
+}
+
+class Deadline {
+ public:
+  explicit Deadline(int timeout_ms) : end_(Clock::now() + std::chrono::milliseconds(timeout_ms)) {}
+  int remaining_ms() const {
+    const auto left = std::chrono::duration_cast<std::chrono::milliseconds>(end_ - Clock::now()).count();
+    return left <= 0 ? 0 : static_cast<int>(std::min<long long>(left, 1 << 30));
+  }
+  bool expired() const { return Clock::now() >= end_; }
+
+ private:
+  Clock::time_point end_;
+};
+
+sockaddr_un abstract_address(const std::string& session, socklen_t* len) {
+  sockaddr_un addr;
+  std::memset(&addr, 0, sizeof(addr));
+  addr.sun_family = AF_UNIX;
+  const std::string name = "msharp." + session;
+  if (name.size() + 1 > sizeof(addr.sun_path)) {
+    throw BootstrapError("bootstrap: session name is too long: " + session);
+  }
+  // Abstract namespace: leading NUL, no file to clean up, gone when the last socket closes.
+  std::memcpy(addr.sun_path + 1, name.data(), name.size());
+  *len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + name.size());
+  return addr;
+}
+
+// Wait until `fd` is readable / writable; false on timeout.
+bool wait_fd(int fd, short events, const Deadline& deadline) {
+  for (;;) {
+    pollfd p{fd, events, 0};
+    const int rc = ::poll(&p, 1, deadline.remaining_ms());
+    if (rc > 0) {
+      return true;
+    }
+    if (rc == 0) {
+      if (deadline.expired()) {
+        return false;
+      }
+      continue;
+    }
+    if (errno != EINTR) {
+      throw BootstrapError(std::string("bootstrap: poll failed: ") + std::strerror(errno));
+    }
+  }
+}
+
+enum class IoStatus { kOk, kTimeout, kClosed };
+
+IoStatus read_exact(int fd, void* buffer, std::size_t bytes, const Deadline& deadline) {
+  auto* p = static_cast<unsigned char*>(buffer);
+  while (bytes > 0) {
+    if (!wait_fd(fd, POLLIN, deadline)) {
+      return IoStatus::kTimeout;
+    }
+    const ssize_t n = ::recv(fd, p, bytes, 0);
+    if (n == 0) {
+      return IoStatus::kClosed;
+    }
+    if (n < 0) {
+      if (errno == EINTR || errno == EAGAIN) {
+        continue;
+      }
+      return IoStatus::kClosed;
+    }
+    p += n;
+    bytes -= static_cast<std::size_t>(n);
+  }
+  return IoStatus::kOk;
+}
+
+IoStatus write_exact(int fd, const void* buffer, std::size_t bytes, const Deadline& deadline) {
+  const auto* p = static_cast<const unsigned char*>(buffer);
+  while (bytes > 0) {
+    if (!wait_fd(fd, POLLOUT, deadline)) {
+      return IoStatus::kTimeout;
+    }
+    const ssize_t n = ::send(fd, p, bytes, MSG_NOSIGNAL);
+    if (n < 0) {
+      if (errno == EINTR || errno == EAGAIN) {
+        continue;
+      }
+      return IoStatus::kClosed;
+    }
+    p += n;
+    bytes -= static_cast<std::size_t>(n);
+  }
+  return IoStatus::kOk;
+}
+
+// Send `count` descriptors (each may be -1 = "none") with a bitmap that says which are real.
+IoStatus send_fds(int sock, const std::vector<int>& fds, const Deadline& deadline) {
+  std::vector<unsigned char> present(fds.size());
+  std::vector<int> real;
+  for (std::size_t i = 0; i < fds.size(); ++i) {
+    present[i] = fds[i] >= 0;
+    if (fds[i] >= 0) {
+      real.push_back(fds[i]);
+    }
+  }
+  if (!wait_fd(sock, POLLOUT, deadline)) {
+    return IoStatus::kTimeout;
+  }
+  msghdr msg;
+  std::memset(&msg, 0, sizeof(msg));
+  iovec iov{present.data(), present.size()};
+  msg.msg_iov = &iov;
+  msg.msg_iovlen = 1;
+  std::vector<unsigned char> control(CMSG_SPACE(sizeof(int) * std::max<std::size_t>(real.size(), 1)));
+  if (!real.empty()) {
+    msg.msg_control = control.data();
+    msg.msg_controllen = CMSG_SPACE(sizeof(int) * real.size());
+    cmsghdr* c = CMSG_FIRSTHDR(&msg);
+    c->cmsg_level = SOL_SOCKET;
+    c->cmsg_type = SCM_RIGHTS;
+    c->cmsg_len = CMSG_LEN(sizeof(int) * real.size());
+    std::memcpy(CMSG_DATA(c), real.data(), sizeof(int) * real.size());
+  }
+  for (;;) {
+    const ssize_t n = ::sendmsg(sock, &msg, MSG_NOSIGNAL);
+    if (n == static_cast<ssize_t>(present.size())) {
+      return IoStatus::kOk;
+    }
+    if (n < 0 && (errno == EINTR || errno == EAGAIN)) {
+      continue;
+    }
+    return IoStatus::kClosed;  // the bitmap is tiny; a short write means a broken socket
+  }
+}
+
+IoStatus recv_fds(int sock, std::size_t count, std::vector<int>* out, const Deadline& deadline) {
+  std::vector<unsigned char> present(count);
+  std::vector<unsigned char> control(CMSG_SPACE(sizeof(int) * std::max<std::size_t>(count, 1)));
+  if (!wait_fd(sock, POLLIN, deadline)) {
+    return IoStatus::kTimeout;
+  }
+  msghdr msg;
+  std::memset(&msg, 0, sizeof(msg));
+  iovec iov{present.data(), present.size()};
+  msg.msg_iov = &iov;
+  msg.msg_iovlen = 1;
+  msg.msg_control = control.data();
+  msg.msg_controllen = control.size();
+  ssize_t n;
+  do {
+    n = ::recvmsg(sock, &msg, MSG_CMSG_CLOEXEC | MSG_WAITALL);
+  } while (n < 0 && errno == EINTR);
+  if (n != static_cast<ssize_t>(count)) {
+    return IoStatus::kClosed;
+  }
+  std::vector<int> real;
+  for (cmsghdr* c = CMSG_FIRSTHDR(&msg); c != nullptr; c = CMSG_NXTHDR(&msg, c)) {
+    if (c->cmsg_level == SOL_SOCKET && c->cmsg_type == SCM_RIGHTS) {
+      const std::size_t n_fd = (c->cmsg_len - CMSG_LEN(0)) / sizeof(int);
+      const std::size_t old = real.size();
+      real.resize(old + n_fd);
+      std::memcpy(real.data() + old, CMSG_DATA(c), n_fd * sizeof(int));
+    }
+  }
+  out->assign(count, -1);
+  std::size_t next = 0;
+  for (std::size_t i = 0; i < count; ++i) {
+    if (present[i]) {
+      if (next >= real.size()) {
+        for (int fd : real) {
+          ::close(fd);
+        }
+        return IoStatus::kClosed;
+      }
+      (*out)[i] = real[next++];
+    }
+  }
+  return IoStatus::kOk;
+}
+
+class SoloBootstrap final : public Bootstrap {
+ public:
+  int rank() const override { return 0; }
+  int world() const override { return 1; }
+  void barrier() override {}
+  void allgather(const void* send, void* recv, std::size_t bytes) override { std::memcpy(recv, send, bytes); }
+  void broadcast(void*, std::size_t, int) override {}
+  std::vector<int> allgather_fd(int fd) override { return {fd >= 0 ? ::dup(fd) : -1}; }
+  int broadcast_fd(int fd, int) override { return fd >= 0 ? ::dup(fd) : -1; }
+  void abort(const std::string&) noexcept override {}
+};
+
+class HubBootstrap final : public Bootstrap {
+ public:
+  explicit HubBootstrap(const BootstrapOptions& opt) : opt_(opt) {
+    if (opt.rank < 0 || opt.rank >= opt.world) {
+      throw BootstrapError("bootstrap: rank " + std::to_string(opt.rank) + " is outside world size " +
+                           std::to_string(opt.world));
+    }
+    if (opt.rank == 0) {
+      listen_and_accept();
+    } else {
+      connect_to_hub();
+    }
+  }
+
+  ~HubBootstrap() override {
+    for (int fd : peers_) {
+      if (fd >= 0) {
+        ::close(fd);
+      }
+    }
+    if (hub_ >= 0) {
+      ::close(hub_);
+    }
+    if (listener_ >= 0) {
+      ::close(listener_);
+    }
+  }
+
+  int rank() const override { return opt_.rank; }
+  int world() const override { return opt_.world; }
+
+  void barrier() override { exchange(kBarrier, nullptr, 0, nullptr, 0, 0); }
+
+  void allgather(const void* send, void* recv, std::size_t bytes) override {
+    exchange(kAllgather, send, bytes, recv, bytes * static_cast<std::size_t>(opt_.world), 0);
+  }
+
+  void broadcast(void* buffer, std::size_t bytes, int root) override {
+    check_root(root);
+    // Gather-then-scatter through the hub keeps one code path; the payloads here are tiny.
+    std::vector<unsigned char> all(bytes * static_cast<std::size_t>(opt_.world));
+    exchange(kBroadcast, buffer, bytes, all.data(), all.size(), static_cast<uint32_t>(root));
+    std::memcpy(buffer, all.data() + bytes * static_cast<std::size_t>(root), bytes);
+  }
+
+  std::vector<int> allgather_fd(int fd) override {
+    const uint32_t seq = ++seq_;
+    check_not_aborted();
+    const Deadline deadline(opt_.timeout_ms);
+    std::vector<int> result(static_cast<std::size_t>(opt_.world), -1);
+    if (opt_.rank == 0) {
+      result[0] = fd >= 0 ? ::dup(fd) : -1;
+      for (int r = 1; r < opt_.world; ++r) {
+        expect_header(r, kFdGather, seq, 1, deadline);
+        std::vector<int> one;
+        guard(recv_fds(peers_[r], 1, &one, deadline), r, kFdGather);
+        result[static_cast<std::size_t>(r)] = one[0];
+      }
+      for (int r = 1; r < opt_.world; ++r) {
+        send_header(peers_[r], kFdGather, seq, static_cast<uint64_t>(opt_.world), r, deadline);
+        guard(send_fds(peers_[r], result, deadline), r, kFdGather);
+      }
+    } else {
+      send_header(hub_, kFdGather, seq, 1, 0, deadline);
+      guard(send_fds(hub_, {fd}, deadline), 0, kFdGather);
+      expect_header(0, kFdGather, seq, static_cast<uint64_t>(opt_.world), deadline);
+      guard(recv_fds(hub_, static_cast<std::size_t>(opt_.world), &result, deadline), 0, kFdGather);
+    }
+    return result;
+  }
+
+  int broadcast_fd(int fd, int root) override {
+    check_root(root);
+    std::vector<int> all = allgather_fd(opt_.rank == root ? fd : -1);
+    int mine = -1;
+    for (int r = 0; r < opt_.world; ++r) {
+      if (r == root) {
+        mine = all[static_cast<std::size_t>(r)];
+      } else if (all[static_cast<std::size_t>(r)] >= 0) {
+        ::close(all[static_cast<std::size_t>(r)]);
+      }
+    }
+    return mine;
+  }
+
+  void abort(const std::string& reason) noexcept override {
+    if (aborted_) {
+      return;
+    }
+    aborted_ = true;
+    abort_reason_ = "rank " + std::to_string(opt_.rank) + " aborted: " + reason;
+    const Deadline deadline(200);
+    Header h;
+    h.op = kAbort;
+    h.rank = opt_.rank;
+    h.bytes = abort_reason_.size();
+    auto tell = [&](int fd) {
+      if (fd >= 0 && write_exact(fd, &h, sizeof(h), deadline) == IoStatus::kOk) {
+        write_exact(fd, abort_reason_.data(), abort_reason_.size(), deadline);
+      }
+    };
+    if (opt_.rank == 0) {
+      for (int r = 1; r < opt_.world; ++r) {
+        tell(peers_[static_cast<std::size_t>(r)]);
+      }
+    } else {
+      tell(hub_);
+    }
+  }
+
+ private:
+  void check_root(int root) const {
+    if (root < 0 || root >= opt_.world) {
+      throw BootstrapError("bootstrap: root " + std::to_string(root) + " is outside the world");
+    }
+  }
+
+  void check_not_aborted() const {
+    if (aborted_) {
+      throw BootstrapError("bootstrap: " + abort_reason_);
+    }
+  }
+
+  [[noreturn]] void fail(const std::string& what, int peer, uint32_t op) {
+    const std::string message = "rank " + std::to_string(opt_.rank) + ": " + what + " rank " + std::to_string(peer) +
+                                " in " + op_name(op);
+    // Pass the news on so that nobody waits for a full timeout on a job that is already lost.
+    if (opt_.rank == 0) {
+      abort(message);
+    }
+    aborted_ = true;
+    abort_reason_ = message;
+    throw BootstrapError("bootstrap: " + message);
+  }
+
+  void guard(IoStatus st, int peer, uint32_t op) {
+    if (st == IoStatus::kTimeout) {
+      fail("timed out waiting for", peer, op);
+    }
+    if (st == IoStatus::kClosed) {
+      fail("lost the connection to", peer, op);
+    }
+  }
+
+  void send_header(int fd, uint32_t op, uint32_t seq, uint64_t bytes, int peer, const Deadline& deadline) {
+    Header h;
+    h.op = op;
+    h.seq = seq;
+    h.rank = opt_.rank;
+    h.bytes = bytes;
+    guard(write_exact(fd, &h, sizeof(h), deadline), peer, op);
+  }
+
+  // Read the next header from `peer` and insist on (op, seq, bytes); handles abort notices.
+  void expect_header(int peer, uint32_t op, uint32_t seq, uint64_t bytes, const Deadline& deadline) {
+    const int fd = opt_.rank == 0 ? peers_[static_cast<std::size_t>(peer)] : hub_;
+    Header h;
+    guard(read_exact(fd, &h, sizeof(h), deadline), peer, op);
+    if (h.magic != kMagic) {
+      fail("received a malformed message from", peer, op);
+    }
+    if (h.op == kAbort) {
+      std::string reason(static_cast<std::size_t>(std::min<uint64_t>(h.bytes, 4096)), '\0');
+      read_exact(fd, reason.data(), reason.size(), deadline);
+      aborted_ = true;
+      abort_reason_ = reason;
+      if (opt_.rank == 0) {
+        forward_abort(peer);
+      }
+      throw BootstrapError("bootstrap: " + reason);
+    }
+    if (h.op != op || h.seq != seq || h.bytes != bytes) {
+      fail(std::string("collective mismatch (got ") + op_name(h.op) + " #" + std::to_string(h.seq) + ", " +
+               std::to_string(h.bytes) + " bytes; expected #" + std::to_string(seq) + ", " + std::to_string(bytes) +
+               " bytes) from",
+           peer, op);
+    }
+  }
+
+  void forward_abort(int origin) noexcept {
+    const Deadline deadline(200);
+    Header h;
+    h.op = kAbort;
+    h.rank = origin;
+    h.bytes = abort_reason_.size();
+    for (int r = 1; r < opt_.world; ++r) {
+      const int fd = peers_[static_cast<std::size_t>(r)];
+      if (r != origin && fd >= 0 && write_exact(fd, &h, sizeof(h), deadline) == IoStatus::kOk) {
+        write_exact(fd, abort_reason_.data(), abort_reason_.size(), deadline);
+      }
+    }
+  }
+
+  // Every rank contributes send_bytes; every rank receives the concatenation (recv_bytes).
+  void exchange(uint32_t op, const void* send, std::size_t send_bytes, void* recv, std::size_t recv_bytes,
+                uint32_t /*root*/) {
+    const uint32_t seq = ++seq_;
+    check_not_aborted();
+    const Deadline deadline(opt_.timeout_ms);
+    if (opt_.rank == 0) {
+      std::vector<unsigned char> all(send_bytes * static_cast<std::size_t>(opt_.world));
+      if (send_bytes) {
+        std::memcpy(all.data(), send, send_bytes);
+      }
+      for (int r = 1; r < opt_.world; ++r) {
+        expect_header(r, op, seq, send_bytes, deadline);
+        if (send_bytes) {
+          guard(read_exact(peers_[static_cast<std::size_t>(r)], all.data() + send_bytes * static_cast<std::size_t>(r),
+                           send_bytes, deadline),
+                r, op);
+        }
+      }
+      for (int r = 1; r < opt_.world; ++r) {
+        send_header(peers_[static_cast<std::size_t>(r)], op, seq, all.size(), r, deadline);
+        if (!all.empty()) {
+          guard(write_exact(peers_[static_cast<std::size_t>(r)], all.data(), all.size(), deadline), r, op);
+        }
+      }
+      if (recv_bytes) {
+        std::memcpy(recv, all.data(), recv_bytes);
+      }
+    } else {
+      send_header(hub_, op, seq, send_bytes, 0, deadline);
+      if (send_bytes) {
+        guard(write_exact(hub_, send, send_bytes, deadline), 0, op);
+      }
+      expect_header(0, op, seq, send_bytes * static_cast<std::size_t>(opt_.world), deadline);
+      if (recv_bytes) {
+        guard(read_exact(hub_, recv, recv_bytes, deadline), 0, op);
+      }
+    }
+  }
+
+  void listen_and_accept() {
+    socklen_t len = 0;
+    const sockaddr_un addr = abstract_address(opt_.session, &len);
+    listener_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+    if (listener_ < 0) {
+      throw BootstrapError(std::string("bootstrap: socket failed: ") + std::strerror(errno));
+    }
+    if (::bind(listener_, reinterpret_cast<const sockaddr*>(&addr), len) != 0) {
+      throw BootstrapError("bootstrap: cannot bind session '" + opt_.session + "': " + std::strerror(errno));
+    }
+    if (::listen(listener_, opt_.world + 8) != 0) {
+      throw BootstrapError(std::string("bootstrap: listen failed: ") + std::strerror(errno));
+    }
+    peers_.assign(static_cast<std::size_t>(opt_.world), -1);
+    const Deadline deadline(opt_.timeout_ms);
+    int joined = 1;
+    while (joined < opt_.world) {
+      if (!wait_fd(listener_, POLLIN, deadline)) {
+        std::string missing;
+        for (int r = 1; r < opt_.world; ++r) {
+          if (peers_[static_cast<std::size_t>(r)] < 0) {
+            missing += (missing.empty() ? "" : ",") + std::to_string(r);
+          }
+        }
+        aborted_ = true;
+        abort_reason_ = "rank 0: timed out waiting for rank(s) " + missing + " to join";
+        abort_peers_after_failed_join();
+        throw BootstrapError("bootstrap: " + abort_reason_);
+      }
+      const int fd = ::accept4(listener_, nullptr, nullptr, SOCK_CLOEXEC);
+      if (fd < 0) {
+        continue;
+      }
+      Header h;
+      const Deadline hello_deadline(std::min(opt_.timeout_ms, 2000));
+      if (read_exact(fd, &h, sizeof(h), hello_deadline) != IoStatus::kOk || h.magic != kMagic || h.op != kHello ||
+          h.rank <= 0 || h.rank >= opt_.world || h.bytes != static_cast<uint64_t>(opt_.world) ||
+          peers_[static_cast<std::size_t>(h.rank)] >= 0) {
+        ::close(fd);  // stranger, duplicate rank, or a rank that disagrees on the world size
+        continue;
+      }
+      peers_[static_cast<std::size_t>(h.rank)] = fd;
+      ++joined;
+    }
+    // Release everyone together.
+    const Deadline go(opt_.timeout_ms);
+    for (int r = 1; r < opt_.world; ++r) {
+      Header h;
+      h.op = kHello;
+      h.rank = 0;
+      h.bytes = static_cast<uint64_t>(opt_.world);
+      guard(write_exact(peers_[static_cast<std::size_t>(r)], &h, sizeof(h), go), r, kHello);
+    }
+  }
+
+  void abort_peers_after_failed_join() noexcept {
+    const Deadline deadline(200);
+    Header h;
+    h.op = kAbort;
+    h.bytes = abort_reason_.size();
+    for (int fd : peers_) {
+      if (fd >= 0 && write_exact(fd, &h, sizeof(h), deadline) == IoStatus::kOk) {
+        write_exact(fd, abort_reason_.data(), abort_reason_.size(), deadline);
+      }
+    }
+  }
+
+  void connect_to_hub() {
+    socklen_t len = 0;
+    const sockaddr_un addr = abstract_address(opt_.session, &len);
+    const Deadline deadline(opt_.timeout_ms);
+    for (;;) {
+      hub_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+      if (hub_ < 0) {
+        throw BootstrapError(std::string("bootstrap: socket failed: ") + std::strerror(errno));
+      }
+      if (::connect(hub_, reinterpret_cast<const sockaddr*>(&addr), len) == 0) {
+        break;
+      }
+      ::close(hub_);
+      hub_ = -1;
+      if (deadline.expired()) {
+        throw BootstrapError("bootstrap: rank " + std::to_string(opt_.rank) + ": timed out connecting to rank 0 (session '" +
+                             opt_.session + "')");
+      }
+      std::this_thread::sleep_for(std::chrono::milliseconds(10));
+    }
+    Header h;
+    h.op = kHello;
+    h.rank = opt_.rank;
+    h.bytes = static_cast<uint64_t>(opt_.world);
+    guard(write_exact(hub_, &h, sizeof(h), deadline), 0, kHello);
+    expect_header(0, kHello, 0, static_cast<uint64_t>(opt_.world), deadline);
+  }
+
+  BootstrapOptions opt_;
+  int listener_ = -1;
+  int hub_ = -1;
+  std::vector<int> peers_;
+  uint32_t seq_ = 0;
+  bool aborted_ = false;
+  std::string abort_reason_;
+};
+
+}  // namespace
+
+double Bootstrap::reduce_max(double value) {
+  const std::vector<double> all = allgather_double(value);
+  return *std::max_element(all.begin(), all.end());
+}
+
+double Bootstrap::reduce_min(double value) {
+  const std::vector<double> all = allgather_double(value);
+  return *std::min_element(all.begin(), all.end());
+}
+
+bool Bootstrap::all_true(bool value) {
+  const unsigned char mine = value ? 1 : 0;
+  std::vector<unsigned char> all(static_cast<std::size_t>(world()));
+  allgather(&mine, all.data(), 1);
+  return std::all_of(all.begin(), all.end(), [](unsigned char v) { return v != 0; });
+}
+
+std::vector<double> Bootstrap::allgather_double(double value) {
+  std::vector<double> all(static_cast<std::size_t>(world()));
+  allgather(&value, all.data(), sizeof(double));
+  return all;
+}
+
+std::vector<uint64_t> Bootstrap::allgather_u64(uint64_t value) {
+  std::vector<uint64_t> all(static_cast<std::size_t>(world()));
+  allgather(&value, all.data(), sizeof(uint64_t));
+  return all;
+}
+
+int Bootstrap::broadcast_int(int value, int root) {
+  broadcast(&value, sizeof(value), root);
+  return value;
+}
+
+std::unique_ptr<Bootstrap> Bootstrap::connect(const BootstrapOptions& options) {
+  if (options.world <= 0) {
+    throw BootstrapError("bootstrap: world size must be positive");
+  }
+  if (options.world == 1) {
+    return std::make_unique<SoloBootstrap>();
+  }
+  return std::make_unique<HubBootstrap>(options);
+}
+
+BootstrapOptions Bootstrap::options_from_env() {
+  BootstrapOptions opt;
+  auto env_int = [](const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
+  };
+  opt.rank = env_int("RANK", 0);
+  opt.world = env_int("WORLD_SIZE", 1);
+  if (const char* s = std::getenv("MSHARP_SESSION"); s != nullptr && *s != '\0') {
+    opt.session = s;
+  } else if (const char* p = std::getenv("MASTER_PORT"); p != nullptr && *p != '\0') {
+    opt.session = std::string("port") + p;
+  }
+  opt.timeout_ms = env_int("MSHARP_BOOTSTRAP_TIMEOUT_MS", opt.timeout_ms);
+  return opt;
+}
+
+}  // namespace msharp

@@ -1,0 +1,362 @@
+#include "msharp/config.h"
+
+#include <cerrno>
+#include <climits>
+#include <cstdlib>
+#include <functional>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+
+#include "msharp/json.h"
+#include "msharp/numerics.h"
+
+namespace msharp {
+namespace {
+
+[[noreturn]] void bad_integer(const std::string& value, const std::string& flag) {
+  throw std::invalid_argument("invalid integer for " + flag + ": " + value);
+}
+
+// strtoull/strtol accept leading whitespace and (for the unsigned form) a minus sign that wraps;
+// std::stoull, which the reference uses, behaves the same way, so both are kept.
+unsigned long long parse_u64(const std::string& value, const std::string& flag) {
+  if (value.empty()) {
+    bad_integer(value, flag);
+  }
+  errno = 0;
+  char* end = nullptr;
+  const unsigned long long parsed = std::strtoull(value.c_str(), &end, 0);
+  if (end == value.c_str() || *end != '\0' || errno == ERANGE) {
+    bad_integer(value, flag);
+  }
+  return parsed;
+}
+
+template <typename Enum>
+Enum choose(const std::string& value, const std::map<std::string, Enum>& table, const std::string& message) {
+  const auto it = table.find(value);
+  if (it == table.end()) {
+    throw std::invalid_argument(message);
+  }
+  return it->second;
+}
+
+}  // namespace
+
+std::size_t parse_size_strict(const std::string& value, const std::string& flag) {
+  return static_cast<std::size_t>(parse_u64(value, flag));
+}
+
+int parse_int_strict(const std::string& value, const std::string& flag) {
+  if (value.empty()) {
+    bad_integer(value, flag);
+  }
+  errno = 0;
+  char* end = nullptr;
+  const long parsed = std::strtol(value.c_str(), &end, 0);
+  if (end == value.c_str() || *end != '\0' || errno == ERANGE || parsed > INT_MAX || parsed < INT_MIN) {
+    bad_integer(value, flag);
+  }
+  return static_cast<int>(parsed);
+}
+
+const char* to_string(Backend b) {
+  switch (b) {
+    case Backend::kLegacy:
+      return "legacy";
+    case Backend::kTmaAsync:
+      return "tma_async";
+    case Backend::kPull:
+      return "pull";
+    case Backend::kSwF32:
+      return "sw_f32";
+  }
+  return "unknown";
+}
+
+const char* to_string(TypeChoice t) {
+  switch (t) {
+    case TypeChoice::kAuto:
+      return "auto";
+    case TypeChoice::kE4M3:
+      return "e4m3";
+    case TypeChoice::kF16:
+      return "f16";
+    case TypeChoice::kBF16:
+      return "bf16";
+  }
+  return "unknown";
+}
+
+const char* to_string(AccChoice a) {
+  switch (a) {
+    case AccChoice::kAuto:
+      return "auto";
+    case AccChoice::kF16:
+      return "f16";
+    case AccChoice::kF32:
+      return "f32";
+  }
+  return "unknown";
+}
+
+const char* to_string(HandleChoice h) {
+  switch (h) {
+    case HandleChoice::kAuto:
+      return "auto";
+    case HandleChoice::kPosixFd:
+      return "posix_fd";
+    case HandleChoice::kFabric:
+      return "fabric";
+  }
+  return "unknown";
+}
+
+TypeChoice resolve_type(const Config& cfg) {
+  if (cfg.types != TypeChoice::kAuto) {
+    return cfg.types;
+  }
+  switch (cfg.sharp_backend) {
+    case Backend::kLegacy:
+    case Backend::kSwF32:
+      return TypeChoice::kE4M3;
+    case Backend::kTmaAsync:
+    case Backend::kPull:
+      return TypeChoice::kF16;
+  }
+  return TypeChoice::kE4M3;
+}
+
+Dtype resolve_dtype(const Config& cfg) {
+  switch (resolve_type(cfg)) {
+    case TypeChoice::kF16:
+      return Dtype::kF16;
+    case TypeChoice::kBF16:
+      return Dtype::kBF16;
+    default:
+      return Dtype::kE4M3;
+  }
+}
+
+AccChoice resolve_acc(const Config& cfg) {
+  if (cfg.sharp_backend == Backend::kSwF32) {
+    return AccChoice::kF32;
+  }
+  if (cfg.sharp_backend == Backend::kTmaAsync) {
+    // the memory-side add of a bulk store-reduce works in the element type
+    return resolve_type(cfg) == TypeChoice::kBF16 ? AccChoice::kF32 : AccChoice::kF16;
+  }
+  if (resolve_type(cfg) == TypeChoice::kE4M3) {
+    return AccChoice::kF16;  // the only accumulator the switch offers for packed FP8
+  }
+  return cfg.acc == AccChoice::kAuto ? AccChoice::kF32 : cfg.acc;
+}
+
+int pattern_id(const std::string& name) {
+  if (name == "reference") {
+    return kPatternReference;
+  }
+  if (name == "seeded") {
+    return kPatternSeeded;
+  }
+  if (name == "tagged") {
+    return kPatternTagged;
+  }
+  return -1;
+}
+
+std::string usage(const char* argv0) {
+  std::ostringstream os;
+  os << "usage: " << argv0 << " --rack-config rack.yaml [--rank-count N]"
+     << " [--rank-selection balanced|prefix] [--sharp-backend legacy|tma_async]"
+     << " [--bytes 1073741824] [--warmup 3] [--iters 20] [--types auto|e4m3|f16]"
+     << " [--reference-check-bytes 16777216] [--init-only] [--json]\n"
+     << "extensions: [--sharp-backend pull|sw_f32] [--types bf16] [--pattern reference|seeded|tagged]"
+     << " [--seed N] [--acc auto|f16|f32] [--handle-type auto|posix_fd|fabric] [--grid N] [--block N]"
+     << " [--unroll N] [--wait-timeout-ms 2000] [--no-pin] [--session NAME] [--reference-geometry]"
+     << " [--cpu-only]\n";
+  return os.str();
+}
+
+Config parse_config(const std::vector<std::string>& args) {
+  Config cfg;
+  const std::string prog = args.empty() ? "mnnvl_sharp_allreduce" : args[0];
+  std::size_t i = 1;
+  auto value_of = [&](const std::string& flag) -> std::string {
+    if (i + 1 >= args.size()) {
+      throw std::invalid_argument("missing value after " + flag);
+    }
+    return args[++i];
+  };
+
+  using Handler = std::function<void(const std::string&)>;
+  const std::map<std::string, Handler> with_value = {
+      {"--rack-config", [&](const std::string& f) { cfg.rack_config_path = value_of(f); }},
+      {"--rank-count", [&](const std::string& f) { cfg.rank_count = parse_int_strict(value_of(f), f); }},
+      {"--rank-selection", [&](const std::string& f) { cfg.rank_selection = value_of(f); }},
+      {"--sharp-backend",
+       [&](const std::string& f) {
+         cfg.sharp_backend = choose<Backend>(
+             value_of(f),
+             {{"legacy", Backend::kLegacy}, {"tma_async", Backend::kTmaAsync}, {"pull", Backend::kPull},
+              {"sw_f32", Backend::kSwF32}},
+             "--sharp-backend must be legacy or tma_async");
+       }},
+      {"--bytes", [&](const std::string& f) { cfg.bytes = parse_size_strict(value_of(f), f); }},
+      {"--warmup", [&](const std::string& f) { cfg.warmup = parse_int_strict(value_of(f), f); }},
+      {"--iters", [&](const std::string& f) { cfg.iters = parse_int_strict(value_of(f), f); }},
+      {"--types",
+       [&](const std::string& f) {
+         cfg.types = choose<TypeChoice>(value_of(f),
+                                        {{"auto", TypeChoice::kAuto}, {"e4m3", TypeChoice::kE4M3},
+                                         {"f16", TypeChoice::kF16}, {"bf16", TypeChoice::kBF16}},
+                                        "--types must be auto, e4m3, or f16");
+       }},
+      {"--reference-check-bytes",
+       [&](const std::string& f) { cfg.reference_check_bytes = parse_size_strict(value_of(f), f); }},
+      {"--pattern", [&](const std::string& f) { cfg.pattern = value_of(f); }},
+      {"--seed", [&](const std::string& f) { cfg.seed = parse_u64(value_of(f), f); }},
+      {"--acc",
+       [&](const std::string& f) {
+         cfg.acc = choose<AccChoice>(value_of(f),
+                                     {{"auto", AccChoice::kAuto}, {"f16", AccChoice::kF16}, {"f32", AccChoice::kF32}},
+                                     "--acc must be auto, f16, or f32");
+       }},
+      {"--handle-type",
+       [&](const std::string& f) {
+         cfg.handle_type = choose<HandleChoice>(
+             value_of(f),
+             {{"auto", HandleChoice::kAuto}, {"posix_fd", HandleChoice::kPosixFd}, {"fabric", HandleChoice::kFabric}},
+             "--handle-type must be auto, posix_fd, or fabric");
+       }},
+      {"--grid", [&](const std::string& f) { cfg.grid = parse_int_strict(value_of(f), f); }},
+      {"--block", [&](const std::string& f) { cfg.block = parse_int_strict(value_of(f), f); }},
+      {"--unroll", [&](const std::string& f) { cfg.unroll = parse_int_strict(value_of(f), f); }},
+      {"--wait-timeout-ms", [&](const std::string& f) { cfg.wait_timeout_ms = parse_int_strict(value_of(f), f); }},
+      {"--session", [&](const std::string& f) { cfg.session = value_of(f); }},
+  };
+  const std::map<std::string, bool Config::*> switches = {
+      {"--init-only", &Config::init_only},
+      {"--json", &Config::json},
+      {"--no-pin", &Config::no_pin},
+      {"--reference-geometry", &Config::reference_geometry},
+      {"--cpu-only", &Config::cpu_only},
+  };
+
+  for (; i < args.size(); ++i) {
+    const std::string& arg = args[i];
+    if (const auto it = with_value.find(arg); it != with_value.end()) {
+      it->second(arg);
+    } else if (const auto sw = switches.find(arg); sw != switches.end()) {
+      cfg.*(sw->second) = true;
+    } else if (arg == "--help" || arg == "-h") {
+      throw std::invalid_argument(usage(prog.c_str()));
+    } else {
+      throw std::invalid_argument("unknown argument: " + arg + "\n" + usage(prog.c_str()));
+    }
+  }
+
+  if (cfg.rack_config_path.empty()) {
+    throw std::invalid_argument("--rack-config is required\n" + usage(prog.c_str()));
+  }
+  if (cfg.bytes == 0 || cfg.bytes % 4 != 0) {
+    throw std::invalid_argument("--bytes must be nonzero and a multiple of 4");
+  }
+  if (cfg.rank_count && *cfg.rank_count <= 0) {
+    throw std::invalid_argument("--rank-count must be >= 1");
+  }
+  if (cfg.rank_selection != "balanced" && cfg.rank_selection != "prefix") {
+    throw std::invalid_argument("--rank-selection must be balanced or prefix");
+  }
+  if (cfg.reference_check_bytes == 0 || cfg.reference_check_bytes % 4 != 0) {
+    throw std::invalid_argument("--reference-check-bytes must be nonzero and a multiple of 4");
+  }
+  if (cfg.reference_check_bytes > cfg.bytes) {
+    throw std::invalid_argument("--reference-check-bytes cannot exceed --bytes");
+  }
+  if (cfg.warmup < 0) {
+    throw std::invalid_argument("--warmup must be >= 0");
+  }
+  if (cfg.iters < 0) {
+    throw std::invalid_argument("--iters must be >= 0");
+  }
+  const TypeChoice type = resolve_type(cfg);
+  if (cfg.sharp_backend == Backend::kLegacy && type != TypeChoice::kE4M3) {
+    throw std::invalid_argument(std::string("--types ") + to_string(type) +
+                                " is not supported with --sharp-backend legacy");
+  }
+  if (cfg.sharp_backend == Backend::kTmaAsync && type == TypeChoice::kE4M3) {
+    throw std::invalid_argument("--types e4m3 is not supported with --sharp-backend tma_async");
+  }
+  if (cfg.sharp_backend == Backend::kSwF32 && type != TypeChoice::kE4M3) {
+    throw std::invalid_argument(std::string("--types ") + to_string(type) +
+                                " is not supported with --sharp-backend sw_f32");
+  }
+  if (cfg.sharp_backend == Backend::kTmaAsync && cfg.bytes % 16 != 0) {
+    throw std::invalid_argument("--bytes must be a multiple of 16 for --sharp-backend tma_async");
+  }
+  if (pattern_id(cfg.pattern) < 0) {
+    throw std::invalid_argument("--pattern must be reference, seeded, or tagged");
+  }
+  if (cfg.acc == AccChoice::kF32 && type == TypeChoice::kE4M3 && cfg.sharp_backend != Backend::kSwF32) {
+    throw std::invalid_argument(
+        "--acc f32 is not available in-switch for e4m3; use --sharp-backend sw_f32");
+  }
+  if (cfg.grid < 0 || cfg.block < 0 || cfg.unroll < 0) {
+    throw std::invalid_argument("--grid, --block and --unroll must be >= 0");
+  }
+  if (cfg.block != 0 && (cfg.block % 32 != 0 || cfg.block > 1024)) {
+    throw std::invalid_argument("--block must be a multiple of 32 and at most 1024");
+  }
+  if (cfg.wait_timeout_ms <= 0) {
+    throw std::invalid_argument("--wait-timeout-ms must be >= 1");
+  }
+  return cfg;
+}
+
+Config parse_config(int argc, const char* const* argv) {
+  std::vector<std::string> args;
+  for (int k = 0; k < argc; ++k) {
+    args.emplace_back(argv[k]);
+  }
+  return parse_config(args);
+}
+
+std::string config_to_json(const Config& cfg) {
+  JsonWriter w;
+  w.begin_object();
+  w.key("rack_config").value(cfg.rack_config_path);
+  w.key("rank_count");
+  if (cfg.rank_count) {
+    w.value(*cfg.rank_count);
+  } else {
+    w.null();
+  }
+  w.key("rank_selection").value(cfg.rank_selection);
+  w.key("sharp_backend").value(to_string(cfg.sharp_backend));
+  w.key("bytes").value(static_cast<uint64_t>(cfg.bytes));
+  w.key("warmup").value(cfg.warmup);
+  w.key("iters").value(cfg.iters);
+  w.key("types").value(to_string(cfg.types));
+  w.key("datatype").value(to_string(resolve_type(cfg)));
+  w.key("reference_check_bytes").value(static_cast<uint64_t>(cfg.reference_check_bytes));
+  w.key("init_only").value(cfg.init_only);
+  w.key("json").value(cfg.json);
+  w.key("pattern").value(cfg.pattern);
+  w.key("seed").value(cfg.seed);
+  w.key("acc").value(to_string(resolve_acc(cfg)));
+  w.key("handle_type").value(to_string(cfg.handle_type));
+  w.key("grid").value(cfg.grid);
+  w.key("block").value(cfg.block);
+  w.key("unroll").value(cfg.unroll);
+  w.key("wait_timeout_ms").value(cfg.wait_timeout_ms);
+  w.key("no_pin").value(cfg.no_pin);
+  w.key("session").value(cfg.session);
+  w.key("reference_geometry").value(cfg.reference_geometry);
+  w.key("cpu_only").value(cfg.cpu_only);
+  w.end_object();
+  return w.str();
+}
+
+}  // namespace msharp

@@ -1,0 +1,210 @@
+#include "msharp/report.h"
+
+#include <iomanip>
+#include <sstream>
+
+#include "msharp/json.h"
+
+namespace msharp {
+
+const char* const kInitLatencyCsvHeader =
+    "rank_count,repeat,sharp_backend,peer_init_ms,peer_init_min_ms,peer_init_median_ms,peer_init_p95_ms,peer_init_max_ms";
+
+double algbw_gb_s(std::size_t bytes, double ms) { return ms > 0.0 ? static_cast<double>(bytes) / (ms * 1e6) : 0.0; }
+
+double busbw_gb_s(std::size_t bytes, double ms, int ranks) {
+  return ranks > 0 ? algbw_gb_s(bytes, ms) * 2.0 * static_cast<double>(ranks - 1) / static_cast<double>(ranks) : 0.0;
+}
+
+double logical_gib_s(std::size_t bytes, double ms, int ranks) {
+  if (ms <= 0.0) {
+    return 0.0;
+  }
+  const double gib = static_cast<double>(ranks) * static_cast<double>(bytes) / (1024.0 * 1024.0 * 1024.0);
+  return gib / (ms / 1000.0);
+}
+
+namespace {
+
+const char* support(bool yes) { return yes ? "supported" : "unsupported"; }
+
+void stats_object(JsonWriter& w, const TimingStats& s) {
+  w.begin_object();
+  w.key("min").value(s.min);
+  w.key("median").value(s.median);
+  w.key("p95").value(s.p95);
+  w.key("max").value(s.max);
+  w.end_object();
+}
+
+std::string hex64(uint64_t v) {
+  std::ostringstream os;
+  os << std::hex << v;
+  return os.str();
+}
+
+}  // namespace
+
+int final_status(const RunReport& r) {
+  if (!r.has_results) {
+    return 0;
+  }
+  if (!hashes_match(r.hashes)) {
+    return 2;
+  }
+  if (r.cfg.pattern == "seeded") {
+    return r.within_tolerance ? 0 : 2;
+  }
+  return r.metrics.exact_mismatches == 0 ? 0 : 2;
+}
+
+std::string json_report(const RunReport& r) {
+  JsonWriter w;
+  w.begin_object();
+  w.key("selected_rank_count").value(static_cast<uint64_t>(r.records.size()));
+  w.key("rank_selection").value(r.cfg.rank_selection);
+  w.key("sharp_backend").value(to_string(r.cfg.sharp_backend));
+  w.key("datatype").value(to_string(resolve_type(r.cfg)));
+  w.key("init_only").value(r.cfg.init_only);
+  w.key("payload_bytes").value(static_cast<uint64_t>(r.cfg.bytes));
+  w.key("allocation_bytes").value(static_cast<uint64_t>(r.allocation_bytes));
+  w.key("input_offset").value(static_cast<uint64_t>(r.input_offset));
+  w.key("output_offset").value(static_cast<uint64_t>(r.output_offset));
+  w.key("multicast_bytes").value(static_cast<uint64_t>(r.multicast_bytes));
+  w.key("datatype_support").begin_object();
+  w.key("e4m3_legacy").value(support(r.caps.sharp_e4m3_supported));
+  w.key("f16_tma_async").value(support(r.caps.sharp_tma_async_supported));
+  w.key("nvfp4").value("unsupported");
+  w.key("mxfp4").value("unsupported");
+  w.end_object();
+  w.key("host_mapping").raw(host_mapping_json(r.records));
+  w.key("peer_init_ms").value(r.peer_init.max);
+  w.key("peer_init_min_ms").value(r.peer_init.min);
+  w.key("peer_init_median_ms").value(r.peer_init.median);
+  w.key("peer_init_p95_ms").value(r.peer_init.p95);
+  w.key("peer_init_max_ms").value(r.peer_init.max);
+  w.key("peer_init_local_ms_by_rank").begin_array();
+  for (double v : r.peer_init_by_rank) {
+    w.value(v);
+  }
+  w.end_array();
+  if (!r.has_results) {
+    w.key("hashes_match").null();
+    w.key("hashes").begin_array().end_array();
+    w.key("semantic_exact_mismatches").null();
+    w.key("f32_requantized_mismatches").null();
+    w.key("f32_max_requantized_ulp_distance").null();
+    w.key("f32_max_abs_error").null();
+    w.key("f32_mean_abs_error").null();
+  } else {
+    w.key("hashes_match").value(hashes_match(r.hashes));
+    w.key("hashes").begin_array();
+    for (uint64_t h : r.hashes) {
+      w.value(hex64(h));
+    }
+    w.end_array();
+    w.key("semantic_exact_mismatches").value(static_cast<uint64_t>(r.metrics.exact_mismatches));
+    w.key("f32_requantized_mismatches").value(static_cast<uint64_t>(r.metrics.requantized_mismatches));
+    w.key("f32_max_requantized_ulp_distance").value(r.metrics.max_requantized_ulp_distance);
+    w.key("f32_max_abs_error").value(r.metrics.max_abs_error);
+    w.key("f32_mean_abs_error").value(r.metrics.mean_abs_error);
+  }
+  w.key("sharp_kernel_ms");
+  stats_object(w, r.device_ms);
+  w.key("collective_wall_ms");
+  stats_object(w, r.wall_ms);
+  // ---- extensions
+  const int n = static_cast<int>(r.records.size());
+  w.key("pattern").value(r.cfg.pattern);
+  w.key("seed").value(r.cfg.seed);
+  w.key("accumulate").value(to_string(resolve_acc(r.cfg)));
+  w.key("handle_type").value(r.handle_kind);
+  w.key("kernel_variant").value(r.kernel_variant);
+  if (!r.bulk_variant.empty()) {
+    w.key("bulk_variant").value(r.bulk_variant);
+  }
+  w.key("bulk_multimem").value(support(r.caps.bulk_multimem_supported));
+  w.key("grid").value(r.grid);
+  w.key("block").value(r.block);
+  w.key("control_init_ms").value(r.control_init_ms);
+  if (r.has_results) {
+    w.key("tolerance_ulp").value(r.tolerance_ulp);
+    w.key("within_tolerance").value(r.within_tolerance);
+    w.key("algbw_gb_s").value(algbw_gb_s(r.cfg.bytes, r.device_ms.median));
+    w.key("busbw_gb_s").value(busbw_gb_s(r.cfg.bytes, r.device_ms.median, n));
+    w.key("effective_logical_bandwidth_gib_s_median").value(logical_gib_s(r.cfg.bytes, r.device_ms.median, n));
+    w.key("status").value(final_status(r));
+  }
+  w.end_object();
+  return w.str();
+}
+
+std::string human_report(const RunReport& r) {
+  std::ostringstream os;
+  const int n = static_cast<int>(r.records.size());
+  os << "mnnvl_sharp_allreduce\n";
+  os << "  selected_rank_count: " << n << "\n";
+  os << "  rank_selection: " << r.cfg.rank_selection << "\n";
+  os << "  sharp_backend: " << to_string(r.cfg.sharp_backend) << "\n";
+  os << "  datatype: " << to_string(resolve_type(r.cfg)) << "\n";
+  os << "  init_only: " << (r.cfg.init_only ? "true" : "false") << "\n";
+  os << "  payload_bytes: " << r.cfg.bytes << "\n";
+  os << "  allocation_bytes: " << r.allocation_bytes << "\n";
+  os << "  input_offset: " << r.input_offset << "\n";
+  os << "  output_offset: " << r.output_offset << "\n";
+  os << "  multicast_bytes: " << r.multicast_bytes << "\n";
+  os << "  vmm_granularity: " << r.vmm_granularity << "\n";
+  os << "  multicast_granularity: " << r.multicast_granularity << "\n";
+  os << "  datatype_support: e4m3_legacy=" << support(r.caps.sharp_e4m3_supported)
+     << " f16_tma_async=" << support(r.caps.sharp_tma_async_supported) << " nvfp4=unsupported mxfp4=unsupported\n";
+  os << "  gpu_mapping:\n";
+  for (const auto& rec : r.records) {
+    os << "    rank " << rec.world_rank << " host=" << rec.host_label << " local_rank=" << rec.local_rank
+       << " gpu=" << rec.gpu_ordinal << " host_numa_id=" << rec.host_numa_id << "\n";
+  }
+  os << "  capabilities: vmm=" << r.caps.vmm_supported << " fabric_handle=" << r.caps.fabric_handle_supported
+     << " multicast=" << r.caps.multicast_supported << "\n";
+  os << "  handle_type: " << r.handle_kind << "\n";
+  os << std::fixed << std::setprecision(3);
+  os << "  peer_init_ms: min=" << r.peer_init.min << " median=" << r.peer_init.median << " p95=" << r.peer_init.p95
+     << " max=" << r.peer_init.max << "\n";
+  os << "  smoke_test: passed\n";
+  if (!r.has_results) {
+    os << "  sharp_allreduce: skipped\n";
+    return os.str();
+  }
+  os << "  replica_hashes:";
+  for (uint64_t h : r.hashes) {
+    os << " 0x" << hex64(h);
+  }
+  os << "\n";
+  os << "  hashes_match: " << (hashes_match(r.hashes) ? "true" : "false") << "\n";
+  os << "  semantic_exact_mismatches: " << r.metrics.exact_mismatches << "\n";
+  os << "  f32_requantized_mismatches: " << r.metrics.requantized_mismatches << "\n";
+  os << "  f32_max_requantized_ulp_distance: " << r.metrics.max_requantized_ulp_distance << "\n";
+  os << "  f32_max_abs_error: " << r.metrics.max_abs_error << "\n";
+  os << "  f32_mean_abs_error: " << r.metrics.mean_abs_error << "\n";
+  os << "  sharp_kernel_ms: min=" << r.device_ms.min << " median=" << r.device_ms.median << " p95=" << r.device_ms.p95
+     << " max=" << r.device_ms.max << "\n";
+  os << "  collective_wall_ms: min=" << r.wall_ms.min << " median=" << r.wall_ms.median << " p95=" << r.wall_ms.p95
+     << " max=" << r.wall_ms.max << "\n";
+  if (r.device_ms.median > 0.0) {
+    os << "  effective_logical_bandwidth_gib_s_median: " << logical_gib_s(r.cfg.bytes, r.device_ms.median, n) << "\n";
+    os << "  algbw_gb_s_median: " << algbw_gb_s(r.cfg.bytes, r.device_ms.median) << "\n";
+    os << "  busbw_gb_s_median: " << busbw_gb_s(r.cfg.bytes, r.device_ms.median, n) << "\n";
+  }
+  os << "  kernel_variant: " << r.kernel_variant << " grid=" << r.grid << " block=" << r.block << "\n";
+  os << "  pattern: " << r.cfg.pattern << " tolerance_ulp=" << r.tolerance_ulp
+     << " within_tolerance=" << (r.within_tolerance ? "true" : "false") << "\n";
+  return os.str();
+}
+
+std::string init_latency_csv_row(int rank_count, int repeat, const std::string& backend, double peer_init_ms,
+                                 double min_ms, double median_ms, double p95_ms, double max_ms) {
+  std::ostringstream os;
+  os << rank_count << "," << repeat << "," << backend << "," << peer_init_ms << "," << min_ms << "," << median_ms << ","
+     << p95_ms << "," << max_ms;
+  return os.str();
+}
+
+}  // namespace msharp

@@ -1,0 +1,65 @@
+// Control plane for one process per GPU on a single host: a star of Unix-domain stream
+// sockets with rank 0 as the hub. It carries what the reference project sends over MPI
+// (64-byte memory handles, barriers, tiny reductions, the final status; call sites listed in
+// the reference at src/runtime.cc:158-162,237,319, src/fabric_memory.cc:111-169 and
+// src/main.cc:91-139,195,478) and, in addition, passes POSIX file descriptors between
+// processes with SCM_RIGHTS, which MPI cannot do and which the POSIX-FD memory handles need.
+//
+// Every call is collective and must be made by all ranks in the same order. Every wait has a
+// deadline; on expiry, on a closed peer, or when any rank calls abort(), all ranks that are
+// inside or later enter a collective get a BootstrapError naming the rank and the reason.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace msharp {
+
+class BootstrapError : public std::runtime_error {
+ public:
+  using std::runtime_error::runtime_error;
+};
+
+struct BootstrapOptions {
+  int rank = 0;
+  int world = 1;
+  std::string session = "default";  // ranks of one job share it; becomes an abstract socket name
+  int timeout_ms = 30000;           // deadline of connect and of every collective
+};
+
+class Bootstrap {
+ public:
+  virtual ~Bootstrap() = default;
+
+  virtual int rank() const = 0;
+  virtual int world() const = 0;
+
+  virtual void barrier() = 0;
+  // recv holds world * bytes_per_rank bytes, ordered by rank.
+  virtual void allgather(const void* send, void* recv, std::size_t bytes_per_rank) = 0;
+  virtual void broadcast(void* buffer, std::size_t bytes, int root) = 0;
+  // One descriptor per rank in, `world` descriptors out (all owned by the caller, including a
+  // duplicate of its own). Ranks that have nothing to share pass -1 and receive -1 in that place.
+  virtual std::vector<int> allgather_fd(int fd) = 0;
+  virtual int broadcast_fd(int fd, int root) = 0;
+  // Tell every other rank that this rank failed; their current or next collective throws.
+  virtual void abort(const std::string& reason) noexcept = 0;
+
+  // Conveniences built on allgather.
+  double reduce_max(double value);
+  double reduce_min(double value);
+  bool all_true(bool value);
+  std::vector<double> allgather_double(double value);
+  std::vector<uint64_t> allgather_u64(uint64_t value);
+  int broadcast_int(int value, int root);
+
+  static std::unique_ptr<Bootstrap> connect(const BootstrapOptions& options);
+  // Options from RANK / WORLD_SIZE / MSHARP_SESSION (or MASTER_PORT) in the environment.
+  static BootstrapOptions options_from_env();
+};
+
+}  // namespace msharp

@@ -1,0 +1,59 @@
+// Per-process communicator state that collective kernels need: a small symmetric control
+// block (arrival counters, per-peer flags, the table of everyone's control-block address,
+// barrier epochs, status words) and the DeviceComm descriptor that is passed to kernels.
+// The reference project keeps no such state: it synchronises ranks on the host only.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <memory>
+#include <string>
+
+#include "msharp/bootstrap.h"
+#include "msharp/device_comm.h"
+#include "msharp/driver_api.h"
+#include "msharp/kernels.h"
+#include "msharp/symm_mem.h"
+
+namespace msharp {
+
+struct DeviceStatus {
+  uint32_t bits = 0;     // StatusBits
+  uint32_t block = 0;    // CTA that reported first
+  uint32_t detail = 0;   // meaning depends on the bit (peer rank, tile, slot<<8|word, ...)
+};
+
+std::string describe_status(const DeviceStatus& status);
+
+class CommContext {
+ public:
+  // Collective. `base` carries device ordinal, handle type and capability bits; its payload and
+  // layout fields are ignored.
+  static std::unique_ptr<CommContext> create(const DriverApi& api, Bootstrap& comm, const SymmOptions& base,
+                                             int wait_timeout_ms);
+  ~CommContext();
+
+  DeviceComm device() const { return device_; }
+  bool has_multicast() const { return block_->mc_base != 0; }
+  // Choose between multimem.red arrivals and per-peer flag stores (the latter needs no multicast).
+  void set_multimem_barrier(bool enabled);
+  void set_timeout_ms(int ms);
+
+  // Blocking reads / resets of the status words (stream must be idle or synchronised by the caller).
+  DeviceStatus read_status() const;
+  void clear_status();
+  // Throws std::runtime_error(describe_status) when a kernel left an error behind.
+  void throw_if_failed(const char* what) const;
+  // Collective: zero counters, flags and epochs on every rank (after a timeout left them uneven).
+  void reset(Bootstrap& comm);
+
+  uint64_t* scratch_u64() const;  // 8-byte device scratch (hash result)
+  void destroy(Bootstrap* comm) noexcept;
+
+ private:
+  CommContext() = default;
+  std::unique_ptr<SymmetricMemory> block_;
+  DeviceComm device_;
+};
+
+}  // namespace msharp

@@ -1,0 +1,82 @@
+// Command-line configuration of the all-reduce benchmark binary.
+//
+// The flag set, defaults and validation messages follow the reference project's parser
+// (src/config.h:9-38, src/config.cc:11-37 strict base-0 integers, :101-109 usage text,
+// :111-179 parsing and cross-flag checks). Flags that the reference does not have are
+// extensions and are listed after the reference flags in usage().
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <optional>
+#include <string>
+#include <vector>
+
+#include "msharp/oracle.h"
+
+namespace msharp {
+
+enum class Backend : int {
+  kLegacy = 0,    // multimem.ld_reduce + multimem.st, FP8 E4M3 (reference name)
+  kTmaAsync = 1,  // bulk-async store-reduce push, F16 (reference name)
+  kPull = 2,      // extension: ld_reduce + st for e4m3 / f16 / bf16 with selectable accumulator
+  kSwF32 = 3,     // extension: FP8 with software float32 accumulation and scales
+};
+
+enum class TypeChoice : int { kAuto = 0, kE4M3 = 1, kF16 = 2, kBF16 = 3 };
+enum class AccChoice : int { kAuto = 0, kF16 = 1, kF32 = 2 };
+enum class HandleChoice : int { kAuto = 0, kPosixFd = 1, kFabric = 2 };
+
+struct Config {
+  // reference flags
+  std::string rack_config_path;
+  std::optional<int> rank_count;
+  std::string rank_selection = "balanced";
+  Backend sharp_backend = Backend::kLegacy;
+  std::size_t bytes = 1073741824ull;
+  int warmup = 3;
+  int iters = 20;
+  TypeChoice types = TypeChoice::kAuto;
+  std::size_t reference_check_bytes = 16777216ull;
+  bool init_only = false;
+  bool json = false;
+  // extensions
+  std::string pattern = "reference";  // reference | seeded | tagged
+  uint64_t seed = 2025;
+  AccChoice acc = AccChoice::kAuto;
+  HandleChoice handle_type = HandleChoice::kAuto;
+  int grid = 0;    // 0 = pick from the device
+  int block = 0;   // 0 = default
+  int unroll = 0;  // 0 = default
+  int wait_timeout_ms = 2000;  // bound of every device-side wait
+  bool no_pin = false;         // skip NUMA pinning
+  std::string session;         // bootstrap session name (default derived from the launcher pid)
+  bool reference_geometry = false;  // run the rank-0-only scalar launch shape of the reference
+  bool cpu_only = false;       // oracle only: no GPU, synthetic ranks reduced on the host
+};
+
+const char* to_string(Backend b);
+const char* to_string(TypeChoice t);
+const char* to_string(AccChoice a);
+const char* to_string(HandleChoice h);
+
+// auto -> e4m3 for legacy / sw_f32, f16 for tma_async / pull.
+TypeChoice resolve_type(const Config& cfg);
+Dtype resolve_dtype(const Config& cfg);
+// auto -> f16 accumulate for e4m3 in-switch, f32 for 16-bit types and for sw_f32.
+AccChoice resolve_acc(const Config& cfg);
+int pattern_id(const std::string& name);  // -1 if unknown
+
+std::string usage(const char* argv0);
+
+// Throws std::invalid_argument with the reference's messages.
+Config parse_config(int argc, const char* const* argv);
+Config parse_config(const std::vector<std::string>& args);  // args[0] is the program name
+
+// Strict integer parsing with base auto-detection (0x.., 0.. octal), whole token consumed.
+std::size_t parse_size_strict(const std::string& value, const std::string& flag);
+int parse_int_strict(const std::string& value, const std::string& flag);
+
+std::string config_to_json(const Config& cfg);
+
+}  // namespace msharp

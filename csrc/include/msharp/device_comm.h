@@ -1,0 +1,43 @@
+// Plain-data description of the per-process control block that kernels use to synchronise
+// with their peers, plus the status codes a kernel can leave behind. Shared by host and
+// device code. The reference project has no device-side synchronisation: it brackets every
+// kernel with MPI_Barrier and a stream synchronise (src/main.cc:91-94,134-136).
+#pragma once
+
+#include <cstdint>
+
+namespace msharp {
+
+constexpr int kMaxWorld = 72;
+constexpr int kMaxBarrierSlots = 2048;  // one slot per CTA of a collective kernel
+constexpr int kCanaryWords = 8;
+
+// Byte offsets inside the (symmetric, multicast-bound) control block of each rank.
+constexpr uint64_t kCtrlCounterOffset = 0;                 // u32[kMaxBarrierSlots]: multimem.red arrivals
+constexpr uint64_t kCtrlFlagOffset = 64ull << 10;          // u32[kMaxBarrierSlots][kMaxWorld]: per-peer flags
+constexpr uint64_t kCtrlPeerTableOffset = 1536ull << 10;   // u64[kMaxWorld]: control-block base of every rank
+constexpr uint64_t kCtrlEpochOffset = kCtrlPeerTableOffset + 4096;    // u32[kMaxBarrierSlots], local use
+constexpr uint64_t kCtrlStatusOffset = kCtrlPeerTableOffset + 32768;  // u32[16], local use
+constexpr uint64_t kCtrlScratchOffset = 1792ull << 10;     // small results (hash, canary verdict)
+constexpr uint64_t kCtrlBytes = 2ull << 20;
+
+enum StatusBits : uint32_t {
+  kStatusOk = 0,
+  kStatusEntryTimeout = 1u << 0,   // a peer did not arrive at the barrier that opens a collective
+  kStatusExitTimeout = 1u << 1,    // a peer did not arrive at the barrier that closes it
+  kStatusCopyTimeout = 1u << 2,    // an mbarrier for a bulk copy did not complete in time
+  kStatusBadArgument = 1u << 3,    // a device-side bounds / alignment check failed; access skipped
+  kStatusFlagTimeout = 1u << 4,    // a tile-ready flag of the fused GEMM did not arrive
+  kStatusCanaryMismatch = 1u << 5,
+};
+
+struct DeviceComm {
+  int rank = 0;
+  int world = 1;
+  unsigned char* ctrl_local = nullptr;  // this rank's control block (unicast mapping)
+  unsigned char* ctrl_mc = nullptr;     // multicast alias of all control blocks, or null
+  unsigned long long timeout_ns = 2000000000ull;
+  int use_multimem_barrier = 0;         // 1: multimem.red arrivals; 0: one flag store per peer
+};
+
+}  // namespace msharp

@@ -1,0 +1,73 @@
+// The slice of the CUDA driver API that symmetric memory needs, as a table of function
+// pointers. The real table is filled from libcuda.so.1 at run time (so this library loads on
+// machines without a driver); tests substitute a host-memory fake that records every call
+// and can be told to fail a chosen call. Call sites in the reference project for the same
+// entry points: src/runtime.cc:203-216 and src/fabric_memory.cc:14-30,40-58,84-212.
+#pragma once
+
+#include <cuda.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace msharp {
+
+struct DriverApi {
+  CUresult (*Init)(unsigned int flags) = nullptr;
+  CUresult (*DriverGetVersion)(int* version) = nullptr;
+  CUresult (*DeviceGet)(CUdevice* device, int ordinal) = nullptr;
+  CUresult (*DeviceGetCount)(int* count) = nullptr;
+  CUresult (*DeviceGetAttribute)(int* value, CUdevice_attribute attrib, CUdevice device) = nullptr;
+  CUresult (*CtxGetCurrent)(CUcontext* ctx) = nullptr;
+  CUresult (*GetErrorName)(CUresult error, const char** name) = nullptr;
+  CUresult (*GetErrorString)(CUresult error, const char** text) = nullptr;
+
+  CUresult (*MemGetAllocationGranularity)(size_t* granularity, const CUmemAllocationProp* prop,
+                                          CUmemAllocationGranularity_flags option) = nullptr;
+  CUresult (*MemCreate)(CUmemGenericAllocationHandle* handle, size_t size, const CUmemAllocationProp* prop,
+                        unsigned long long flags) = nullptr;
+  CUresult (*MemRelease)(CUmemGenericAllocationHandle handle) = nullptr;
+  CUresult (*MemExportToShareableHandle)(void* shareable, CUmemGenericAllocationHandle handle,
+                                         CUmemAllocationHandleType type, unsigned long long flags) = nullptr;
+  CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle* handle, void* os_handle,
+                                           CUmemAllocationHandleType type) = nullptr;
+  CUresult (*MemAddressReserve)(CUdeviceptr* ptr, size_t size, size_t alignment, CUdeviceptr addr,
+                                unsigned long long flags) = nullptr;
+  CUresult (*MemAddressFree)(CUdeviceptr ptr, size_t size) = nullptr;
+  CUresult (*MemMap)(CUdeviceptr ptr, size_t size, size_t offset, CUmemGenericAllocationHandle handle,
+                     unsigned long long flags) = nullptr;
+  CUresult (*MemUnmap)(CUdeviceptr ptr, size_t size) = nullptr;
+  CUresult (*MemSetAccess)(CUdeviceptr ptr, size_t size, const CUmemAccessDesc* desc, size_t count) = nullptr;
+
+  CUresult (*MulticastGetGranularity)(size_t* granularity, const CUmulticastObjectProp* prop,
+                                      CUmulticastGranularity_flags option) = nullptr;
+  CUresult (*MulticastCreate)(CUmemGenericAllocationHandle* handle, const CUmulticastObjectProp* prop) = nullptr;
+  CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle handle, CUdevice device) = nullptr;
+  CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle mc_handle, size_t mc_offset,
+                               CUmemGenericAllocationHandle mem_handle, size_t mem_offset, size_t size,
+                               unsigned long long flags) = nullptr;
+  CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle handle, CUdevice device, size_t mc_offset,
+                              size_t size) = nullptr;
+
+  CUresult (*MemcpyDtoH)(void* dst, CUdeviceptr src, size_t bytes) = nullptr;
+  CUresult (*MemcpyHtoD)(CUdeviceptr dst, const void* src, size_t bytes) = nullptr;
+
+  CUresult (*ModuleLoadDataEx)(CUmodule* module, const void* image, unsigned int num_options, CUjit_option* options,
+                               void** values) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule module) = nullptr;
+
+  bool is_fake = false;
+};
+
+// Loads libcuda.so.1 on first use. Throws std::runtime_error when no driver is installed.
+const DriverApi& real_driver();
+bool real_driver_available();
+
+std::string driver_error_text(const DriverApi& api, CUresult code);
+
+// Throws std::runtime_error("<expr> failed: NAME: text") like the reference's MNNVL_CHECK_CU.
+void check_driver(const DriverApi& api, CUresult code, const char* expression);
+
+#define MSHARP_CU(api, call) ::msharp::check_driver((api), (api).call, #call)
+
+}  // namespace msharp

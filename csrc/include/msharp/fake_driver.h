@@ -1,0 +1,35 @@
+// Host-memory stand-in for the CUDA driver, for tests that run without a GPU.
+//
+// Allocations are memfd files, so exported POSIX descriptors really can be passed to another
+// process and mapped there; address reservations are PROT_NONE mmaps and cuMemMap places the
+// file at the reserved address, so "device pointers" are ordinary host pointers that the
+// canary check can read. Multicast objects are bookkeeping only (nothing replicates stores).
+// Every call is logged, and a chosen call can be made to fail with a chosen CUresult: that is
+// how failure handling of the symmetric-memory set-up is exercised without touching a GPU.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "msharp/driver_api.h"
+
+namespace msharp {
+
+const DriverApi& fake_driver();
+
+// Forget all state (handles, mappings, log, failure plan) and set the device count.
+void fake_driver_reset(int device_count = 8);
+void fake_driver_set_attribute(CUdevice_attribute attribute, int value);
+// The `nth` call (1 = next) of driver function `name` (for example "cuMemMap") returns `code`.
+void fake_driver_fail_call(const std::string& name, int nth, CUresult code);
+std::vector<std::string> fake_driver_call_log();
+// Number of live handles / reservations / mappings: all zero after a clean teardown.
+struct FakeDriverLeaks {
+  int handles = 0;
+  int reservations = 0;
+  int mappings = 0;
+  int multicast_bindings = 0;
+};
+FakeDriverLeaks fake_driver_leaks();
+
+}  // namespace msharp

@@ -1,0 +1,72 @@
+// Host-callable launchers of the device kernels. Every launcher only enqueues work on the
+// given stream and throws std::runtime_error if the launch itself is refused; results and
+// device-side failures (status bits of device_comm.h) are read by the caller after a
+// stream synchronise.
+//
+// Counterparts in the reference project's src/sharp_kernels.{h,cu}: deterministic init
+// (:76-90), proxy fence kernels (:92-106), the FP8 ld_reduce/st all-reduce (:108-120), the
+// F16 bulk store-reduce all-reduce (:122-161), canary (:163-168), hash (:179-187).
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "msharp/device_comm.h"
+#include "msharp/oracle.h"
+
+namespace msharp {
+
+struct PeerPointers {
+  uint64_t ptr[kMaxWorld];
+};
+
+struct LaunchShape {
+  int grid = 0;    // 0 = as many CTAs as stay resident (capped by the work and by kMaxBarrierSlots)
+  int block = 0;   // 0 = kernel default
+  int unroll = 0;  // 0 = kernel default (pull kernels: 1, 2, 4 or 8 vectors in flight per thread)
+};
+
+void check_cuda(cudaError_t code, const char* expression);
+#define MSHARP_CUDA(call) ::msharp::check_cuda((call), #call)
+
+// ---- utility kernels
+void launch_init_pattern(Dtype dtype, int pattern, uint64_t seed, int rank, void* dst, std::size_t bytes,
+                         cudaStream_t stream);
+void launch_poison_fill(void* dst, std::size_t bytes, cudaStream_t stream);  // 0xFF bytes: NaN in e4m3/f16/bf16
+void launch_alias_fence(cudaStream_t stream);
+void launch_async_proxy_fence(cudaStream_t stream);
+void launch_canary_write(uint32_t* self_slot_words, int rank, cudaStream_t stream);
+// Reads the canary of every slot through the unicast mappings after a device barrier (which
+// itself exercises the multicast alias when the communicator uses multimem arrivals).
+void launch_canary_verify(const DeviceComm& comm, const PeerPointers& slots, cudaStream_t stream);
+// XOR-of-mixed-words hash of `bytes` (multiple of 4) into *out_hash (device, 8 bytes; zeroed here).
+void launch_hash(const void* data, std::size_t bytes, uint64_t* out_hash, cudaStream_t stream);
+
+// ---- all-reduce kernels (in place over `bytes` of every rank's buffer)
+enum class PullAcc : int { kNative = 0, kF32 = 1 };
+// K1/K2: every rank reduces its 1/world slice with multimem.ld_reduce and writes it to all
+// replicas with multimem.st. `mc_data` is the multicast alias of the buffers; for a world of
+// one rank pass the local pointer (a plain copy pass is run in its place).
+void launch_allreduce_pull(const DeviceComm& comm, Dtype dtype, PullAcc acc, void* mc_data, std::size_t bytes,
+                           const LaunchShape& shape, cudaStream_t stream);
+// The reference's launch shape: one rank, <=4096x256 threads, one 4-byte ld_reduce + st per
+// step, no device barrier (the caller brackets it with host barriers). For comparisons only.
+void launch_allreduce_reference_geometry(Dtype dtype, void* mc_data, std::size_t bytes, cudaStream_t stream);
+// K3: FP8 with software float32 accumulation: out = sat_e4m3(out_scale_inv * sum_r in_scale[r] * x_r).
+// Reads all peers' buffers through unicast mappings, writes through the multicast alias when
+// `mc_data` is non-null, else through the unicast mappings.
+void launch_allreduce_sw_f32(const DeviceComm& comm, const PeerPointers& slots, void* mc_data, std::size_t bytes,
+                             const float* in_scales_device, float out_scale_inv, const LaunchShape& shape,
+                             cudaStream_t stream);
+// K4: bulk-async push. out[r] = sum over ranks of in[rank], built as "own copy, barrier, then
+// cp.reduce.async.bulk into every peer's output". bytes must be a multiple of 16.
+void launch_allreduce_bulk_push(const DeviceComm& comm, Dtype dtype, const void* local_input,
+                                const PeerPointers& outputs, std::size_t bytes, const LaunchShape& shape,
+                                cudaStream_t stream);
+bool bulk_multimem_compiled();  // whether this build contains the multimem bulk form
+
+int device_sm_count();
+
+}  // namespace msharp

@@ -1,0 +1,59 @@
+// Run summary and its three renderings: the single JSON line, the human report and one row of
+// init_latency.csv. Key order and meanings of the reference project's keys are kept
+// (JSON: src/main.cc:295-354 with host_mapping from src/runtime.cc:384-402; human report:
+// src/main.cc:227-283; CSV header: scripts/run_init_sweep.py:143-152). Keys that the
+// reference does not have are appended after its last key.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "msharp/config.h"
+#include "msharp/oracle.h"
+#include "msharp/topology.h"
+
+namespace msharp {
+
+struct RunReport {
+  Config cfg;
+  CapabilityInfo caps;
+  std::vector<RankMappingRecord> records;
+  std::size_t allocation_bytes = 0;
+  std::size_t input_offset = 0;
+  std::size_t output_offset = 0;
+  std::size_t multicast_bytes = 0;
+  std::size_t vmm_granularity = 0;
+  std::size_t multicast_granularity = 0;
+  TimingStats peer_init;
+  std::vector<double> peer_init_by_rank;
+  // absent for --init-only
+  bool has_results = false;
+  std::vector<uint64_t> hashes;
+  PrecisionMetrics metrics;
+  TimingStats device_ms;
+  TimingStats wall_ms;
+  // extensions
+  std::string handle_kind;
+  std::string bulk_variant;  // "multimem", "unicast_fanout" or "" (not a bulk run)
+  std::string kernel_variant;
+  int tolerance_ulp = 0;
+  bool within_tolerance = true;
+  int grid = 0;
+  int block = 0;
+  double control_init_ms = 0.0;
+};
+
+double algbw_gb_s(std::size_t bytes, double ms);                  // bytes / time, 1e9 bytes per GB
+double busbw_gb_s(std::size_t bytes, double ms, int ranks);       // algbw * 2 (n-1) / n
+double logical_gib_s(std::size_t bytes, double ms, int ranks);    // ranks * bytes / time in GiB/s
+
+std::string json_report(const RunReport& r);
+std::string human_report(const RunReport& r);
+// 0 = pass, 2 = replicas differ or the result is outside the stated tolerance.
+int final_status(const RunReport& r);
+
+extern const char* const kInitLatencyCsvHeader;
+std::string init_latency_csv_row(int rank_count, int repeat, const std::string& backend, double peer_init_ms,
+                                 double min_ms, double median_ms, double p95_ms, double max_ms);
+
+}  // namespace msharp

@@ -1,0 +1,101 @@
+// Symmetric memory: every rank allocates the same amount of shareable device memory, all
+// ranks map all allocations at `uc_base + rank * alloc_bytes` (the unicast slot table), and a
+// multicast object bound to a sub-range of every allocation is mapped at `mc_base`, so that
+// multimem instructions on that alias reach all replicas through the NVSwitch.
+//
+// The recipe and its timed "peer init" phase follow the reference project's
+// src/fabric_memory.cc (layout :93-107, create :109, timed export/exchange/import/reserve/map
+// :111-142, multicast create/add/bind/map with a barrier after each step :144-170, teardown
+// order :173-212). Differences: handles are POSIX file descriptors passed over the bootstrap
+// (fabric handles remain selectable), a world of one rank gets no multicast object (the driver
+// refuses to create one for a single device), and every step that can fail on one rank is
+// followed by an agreement so that all ranks raise together instead of waiting for a rank
+// that is gone.
+#pragma once
+
+#include <cstddef>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "msharp/bootstrap.h"
+#include "msharp/config.h"
+#include "msharp/driver_api.h"
+
+namespace msharp {
+
+enum class RegionLayout : int {
+  kSingle = 0,       // one region: input == output == multicast range (in-place collectives)
+  kInputOutput = 1,  // input region followed by output region; multicast covers the output only
+};
+
+struct SymmOptions {
+  std::size_t payload_bytes = 0;
+  RegionLayout layout = RegionLayout::kSingle;
+  HandleChoice handle_type = HandleChoice::kAuto;
+  bool want_multicast = true;
+  int device_ordinal = 0;
+  CUdevice cu_device = 0;
+  bool posix_fd_supported = true;
+  bool fabric_supported = false;
+  bool multicast_supported = true;
+};
+
+std::size_t align_up(std::size_t value, std::size_t alignment);  // overflow-checked
+
+class SymmetricMemory {
+ public:
+  // Collective over `comm`. The device must be current on the calling thread.
+  static std::unique_ptr<SymmetricMemory> create(const DriverApi& api, Bootstrap& comm, const SymmOptions& options);
+  ~SymmetricMemory();
+  SymmetricMemory(const SymmetricMemory&) = delete;
+  SymmetricMemory& operator=(const SymmetricMemory&) = delete;
+
+  // Not collective by itself: the caller brackets it with barriers so that no kernel on any
+  // rank still uses a mapping that is being removed. Safe to call twice and after partial set-up.
+  void destroy() noexcept;
+
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+
+  std::size_t payload_bytes = 0;
+  std::size_t alloc_bytes = 0;
+  std::size_t input_offset = 0;
+  std::size_t output_offset = 0;
+  std::size_t multicast_bytes = 0;
+  std::size_t multicast_bind_offset = 0;
+  std::size_t vmm_granularity = 0;
+  std::size_t multicast_granularity = 0;
+  CUdeviceptr uc_base = 0;
+  std::vector<CUdeviceptr> uc_slots;
+  CUdeviceptr mc_base = 0;  // 0 when there is no multicast alias
+  bool multicast_bound = false;
+  double peer_init_local_ms = 0.0;
+  std::vector<double> peer_init_all_ms;
+  std::string handle_kind;  // "posix_fd", "fabric" or "none" (single rank)
+
+  CUdeviceptr input_ptr(int rank) const { return uc_slots[static_cast<std::size_t>(rank)] + input_offset; }
+  CUdeviceptr output_ptr(int rank) const { return uc_slots[static_cast<std::size_t>(rank)] + output_offset; }
+  // Multicast address of byte `offset_in_output` of the output region (0 if no alias).
+  CUdeviceptr mc_output_ptr() const { return mc_base == 0 ? 0 : mc_base + (output_offset - multicast_bind_offset); }
+
+  void copy_to_host(void* dst, int slot_rank, std::size_t offset, std::size_t bytes) const;
+  void copy_from_host(int slot_rank, std::size_t offset, const void* src, std::size_t bytes) const;
+
+ private:
+  SymmetricMemory(const DriverApi& api, int rank, int world) : api_(api), rank_(rank), world_(world) {}
+  void build(Bootstrap& comm, const SymmOptions& options);
+
+  const DriverApi& api_;
+  int rank_ = 0;
+  int world_ = 1;
+  CUdevice device_ = 0;
+  CUmemGenericAllocationHandle local_handle_ = 0;
+  std::vector<CUmemGenericAllocationHandle> imported_;  // index = rank; 0 for self / not imported
+  std::vector<bool> slot_mapped_;
+  CUmemGenericAllocationHandle multicast_handle_ = 0;
+  bool mc_mapped_ = false;
+  std::size_t uc_reserved_bytes_ = 0;
+};
+
+}  // namespace msharp

@@ -1,0 +1,88 @@
+// Who runs where: matching this process to a tray of the rack inventory, capability query,
+// cross-rank validation of the rank -> (host, GPU) mapping, and NUMA pinning.
+//
+// Behaviour follows the reference project's runtime layer (paths within it):
+//   src/runtime.cc:148-197  host label match (MNNVL_HOST_LABEL override), plan checks, local rank
+//   src/runtime.cc:199-230  capability attributes; FP4 types are always reported unsupported
+//   src/runtime.cc:232-307  gathered mapping records validated against the plan
+//   src/runtime.cc:309-324  capability consensus over all ranks
+//   src/runtime.cc:49-80,326-351  cpulist parsing and sched_setaffinity to the GPU's NUMA node
+// The control plane is the Unix-socket bootstrap instead of MPI, so "MPI" in the reference's
+// messages reads "launch" here.
+#pragma once
+
+#include <string>
+#include <vector>
+
+#include "msharp/bootstrap.h"
+#include "msharp/config.h"
+#include "msharp/driver_api.h"
+#include "msharp/rack.h"
+
+namespace msharp {
+
+struct RankInfo {
+  int world_rank = 0;
+  int world_size = 1;
+  int local_rank = 0;
+  int local_size = 1;
+  int rack_index = 0;
+  int rack_count = 1;
+  std::string host_label;
+  std::string control_hostname;
+  int ssh_port = kDefaultSshPort;
+  std::string os_hostname;
+  int gpu_ordinal = 0;
+  int host_numa_id = -1;
+  CUdevice cu_device = 0;
+};
+
+struct CapabilityInfo {
+  bool vmm_supported = false;
+  bool posix_fd_handle_supported = false;
+  bool fabric_handle_supported = false;
+  bool multicast_supported = false;
+  bool sharp_e4m3_supported = false;       // "e4m3_legacy" in reports
+  bool sharp_tma_async_supported = false;  // "f16_tma_async" in reports
+  bool bulk_multimem_supported = false;    // driver can assemble multimem.cp.reduce.async.bulk
+  bool nvfp4_supported = false;            // never: reported, not implemented
+  bool mxfp4_supported = false;
+  int driver_version = 0;
+};
+
+struct RankMappingRecord {  // fixed-size, trivially copyable: gathered as raw bytes
+  int world_rank = 0;
+  int local_rank = 0;
+  int rack_index = 0;
+  int gpu_ordinal = 0;
+  int host_numa_id = -1;
+  char host_label[128] = {0};
+  char os_hostname[128] = {0};
+};
+
+std::string os_hostname();
+
+// Host-only part: which tray is this process on, and does that agree with the plan?
+// `host_label_override` replaces the OS hostname (the MNNVL_HOST_LABEL variable); the label
+// "localhost" in the inventory matches any machine.
+RankInfo discover_rank_info(int world_rank, int world_size, const RackConfig& rack, const RankPlan& plan,
+                            const std::string& host_label_override = "");
+
+// cuInit + device lookup + attributes. The caller has already made the device current.
+CapabilityInfo query_capabilities(const DriverApi& api, RankInfo* rank);
+
+// Ask the driver to assemble a PTX 9.1 module that uses multimem.cp.reduce.async.bulk.
+bool probe_bulk_multimem(const DriverApi& api, std::string* detail);
+
+std::vector<RankMappingRecord> gather_rank_mappings(Bootstrap& comm, const RankInfo& rank);
+void validate_rank_mappings(const std::vector<RankMappingRecord>& records, const RackConfig& rack,
+                            const RankPlan& plan);
+// Throws on every rank when any rank lacks what `backend` needs.
+void validate_capabilities(Bootstrap& comm, const CapabilityInfo& caps, Backend backend, int world_size);
+
+std::vector<int> parse_cpu_list(const std::string& text);
+void pin_thread_to_numa(int numa_id);
+
+std::string host_mapping_json(const std::vector<RankMappingRecord>& records);
+
+}  // namespace msharp

@@ -1,0 +1,536 @@
+// All-reduce kernels for sm_100a. Every kernel is one launch per rank that contains its own
+// cross-GPU barriers, so a CUDA-event pair around the launch times the whole collective.
+//
+//  pull       multimem.ld_reduce (reduction inside the NVSwitch) + multimem.st, 16 bytes per
+//             instruction, each rank owning 1/world of the buffer. The reference's kernel for
+//             the same job (src/sharp_kernels.cu:108-120) is launched by rank 0 alone and moves
+//             4 bytes per instruction.
+//  sw_f32     FP8 E4M3 with float32 accumulation and scales in registers: the switch cannot
+//             accumulate packed FP8 in float32, so each CTA fetches its chunk from every peer
+//             with ordinary loads and only the result goes through the switch (multimem.st).
+//  bulk push  bulk-async (TMA engine) store-reduce from shared memory into every replica.
+//             The reference (src/sharp_kernels.cu:122-161) uses the multicast form
+//             multimem.cp.reduce.async.bulk, one 4 KiB tile at a time with a full wait after
+//             each; here tiles are pipelined through a shared-memory ring, and where the
+//             multicast form cannot be assembled the same add is sent to each peer with the
+//             unicast cp.reduce.async.bulk.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+#include "device_comm.cuh"
+#include "msharp/kernels.h"
+
+#ifndef MSHARP_HAS_BULK_MULTIMEM
+#define MSHARP_HAS_BULK_MULTIMEM 0
+#endif
+
+namespace msharp {
+namespace {
+
+using dev::Vec4;
+
+void check_launch(const char* kernel) {
+  const cudaError_t err = cudaPeekAtLastError();
+  if (err != cudaSuccess) {
+    throw std::runtime_error(std::string(kernel) + " launch failed: " + cudaGetErrorString(err));
+  }
+}
+
+// ------------------------------------------------------------------------------------ pull
+template <int KIND, int UNROLL>
+__global__ void __launch_bounds__(1024)
+allreduce_pull_kernel(DeviceComm comm, uint4* __restrict__ data, std::size_t vectors, std::size_t tail_words) {
+  constexpr bool kLocal = KIND == dev::kReduceLocalCopy;
+  if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
+    return;
+  }
+  dev::fence_proxy_alias();  // inputs were written through the unicast mapping
+
+  const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
+  const std::size_t begin = std::min(vectors, per_rank * comm.rank);
+  const std::size_t end = std::min(vectors, begin + per_rank);
+  const std::size_t step = static_cast<std::size_t>(blockDim.x) * UNROLL;
+  for (std::size_t base = begin + static_cast<std::size_t>(blockIdx.x) * step; base < end;
+       base += static_cast<std::size_t>(gridDim.x) * step) {
+    Vec4 v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const std::size_t i = base + static_cast<std::size_t>(u) * blockDim.x + threadIdx.x;
+      if (i < end) {
+        v[u] = dev::ld_reduce_v4<KIND>(data + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const std::size_t i = base + static_cast<std::size_t>(u) * blockDim.x + threadIdx.x;
+      if (i < end) {
+        dev::st_all_v4<kLocal>(data + i, v[u]);
+      }
+    }
+  }
+  // up to three 32-bit words beyond the last full vector: the last rank takes them
+  if (comm.rank == comm.world - 1 && blockIdx.x == 0 && threadIdx.x < tail_words) {
+    uint32_t* word = reinterpret_cast<uint32_t*>(data + vectors) + threadIdx.x;
+    dev::st_all_b32<kLocal>(word, dev::ld_reduce_b32<KIND>(word));
+  }
+  dev::fence_proxy_alias();
+  dev::grid_peers_barrier(comm, kStatusExitTimeout);
+}
+
+template <int KIND>
+__global__ void allreduce_reference_geometry_kernel(uint32_t* mc_words, std::size_t words) {
+  const std::size_t stride = static_cast<std::size_t>(gridDim.x) * blockDim.x;
+  for (std::size_t i = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < words; i += stride) {
+    dev::st_all_b32<false>(mc_words + i, dev::ld_reduce_b32<KIND>(mc_words + i));
+  }
+}
+
+// ------------------------------------------------------------------------------------ sw_f32
+__device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// four packed E4M3 -> four floats (hardware conversion is exact)
+__device__ __forceinline__ void e4m3x4_to_f32(uint32_t packed, float* out) {
+  uint32_t lo, hi;
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+      : "=r"(lo), "=r"(hi) : "r"(packed));
+  const __half2 l = *reinterpret_cast<const __half2*>(&lo);
+  const __half2 h = *reinterpret_cast<const __half2*>(&hi);
+  out[0] = __low2float(l);
+  out[1] = __high2float(l);
+  out[2] = __low2float(h);
+  out[3] = __high2float(h);
+}
+
+// four floats -> four packed E4M3, round to nearest even, saturate to +-448
+__device__ __forceinline__ uint32_t f32x4_to_e4m3(const float* in) {
+  uint32_t packed;
+  asm("{\n\t.reg .b16 a, b;\n\tcvt.rn.satfinite.e4m3x2.f32 a, %2, %1;\n\tcvt.rn.satfinite.e4m3x2.f32 b, %4, %3;\n\t"
+      "mov.b32 %0, {a, b};\n\t}"
+      : "=r"(packed) : "f"(in[0]), "f"(in[1]), "f"(in[2]), "f"(in[3]));
+  return packed;
+}
+
+template <bool USE_MC>
+__global__ void __launch_bounds__(512)
+allreduce_sw_f32_kernel(DeviceComm comm, PeerPointers slots, uint4* mc_data, std::size_t vectors,
+                        std::size_t tail_words, const float* __restrict__ in_scales, float out_scale_inv) {
+  __shared__ float s_scale[kMaxWorld];
+  for (int r = threadIdx.x; r < comm.world; r += blockDim.x) {
+    s_scale[r] = in_scales != nullptr ? in_scales[r] : 1.0f;
+  }
+  if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
+    return;
+  }
+  const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
+  const std::size_t begin = std::min(vectors, per_rank * comm.rank);
+  const std::size_t end = std::min(vectors, begin + per_rank);
+  const std::size_t stride = static_cast<std::size_t>(gridDim.x) * blockDim.x;
+
+  auto reduce_word = [&](std::size_t word_index) -> uint32_t {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < comm.world; ++r) {
+      const volatile uint32_t* src = reinterpret_cast<const volatile uint32_t*>(slots.ptr[r]);
+      float x[4];
+      e4m3x4_to_f32(src[word_index], x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc[k] += s_scale[r] * x[k];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc[k] *= out_scale_inv;
+    }
+    return f32x4_to_e4m3(acc);
+  };
+
+  for (std::size_t i = begin + static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < end; i += stride) {
+    float acc[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      acc[k] = 0.f;
+    }
+    // four peer loads are issued back to back before the first is consumed, so that their
+    // NVLink round trips overlap; the sum still runs in rank order (it matches the host oracle)
+    for (int r0 = 0; r0 < comm.world; r0 += 4) {
+      uint4 q[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (r0 + j < comm.world) {
+          q[j] = ld_peer_v4(reinterpret_cast<const uint4*>(slots.ptr[r0 + j]) + i);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (r0 + j < comm.world) {
+          const float s = s_scale[r0 + j];
+          float x[16];
+          e4m3x4_to_f32(q[j].x, x);
+          e4m3x4_to_f32(q[j].y, x + 4);
+          e4m3x4_to_f32(q[j].z, x + 8);
+          e4m3x4_to_f32(q[j].w, x + 12);
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            acc[k] += s * x[k];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      acc[k] *= out_scale_inv;
+    }
+    Vec4 out;
+    out.x = f32x4_to_e4m3(acc);
+    out.y = f32x4_to_e4m3(acc + 4);
+    out.z = f32x4_to_e4m3(acc + 8);
+    out.w = f32x4_to_e4m3(acc + 12);
+    if constexpr (USE_MC) {
+      dev::st_all_v4<false>(mc_data + i, out);
+    } else {
+      for (int r = 0; r < comm.world; ++r) {
+        dev::st_all_v4<true>(reinterpret_cast<uint4*>(slots.ptr[r]) + i, out);
+      }
+    }
+  }
+  if (comm.rank == comm.world - 1 && blockIdx.x == 0 && threadIdx.x < tail_words) {
+    const std::size_t word = vectors * 4 + threadIdx.x;
+    const uint32_t out = reduce_word(word);
+    if constexpr (USE_MC) {
+      dev::st_all_b32<false>(reinterpret_cast<uint32_t*>(mc_data) + word, out);
+    } else {
+      for (int r = 0; r < comm.world; ++r) {
+        dev::st_all_b32<true>(reinterpret_cast<uint32_t*>(slots.ptr[r]) + word, out);
+      }
+    }
+  }
+  dev::fence_proxy_alias();
+  dev::grid_peers_barrier(comm, kStatusExitTimeout);
+}
+
+// ------------------------------------------------------------------------------------ bulk push
+constexpr int kBulkStages = 4;
+constexpr int kBulkTileBytes = 16384;
+constexpr int kBulkThreads = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded wait on an mbarrier phase; false when the deadline passed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns) {
+  const unsigned long long start = dev::global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      uint32_t done;
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+      if (done) {
+        return true;
+      }
+    }
+    if (dev::global_timer_ns() - start > timeout_ns) {
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+template <int DT>  // 1 = f16, 2 = bf16
+__device__ __forceinline__ void bulk_reduce_add(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  if constexpr (DT == 1) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;"
+                 ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+  } else {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
+                 ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+  }
+}
+
+#if MSHARP_HAS_BULK_MULTIMEM
+__device__ __forceinline__ void bulk_reduce_add_multimem_f16(void* mc_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("multimem.cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;"
+               ::"l"(mc_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+#endif
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Tiles are dealt to CTAs round-robin, identically on every rank: CTA b of every rank touches
+// the same tiles, so the per-CTA barrier between the two phases is all the ordering needed
+// between "owner wrote its own copy" and "peers add into it".
+template <int DT>
+__global__ void __launch_bounds__(kBulkThreads)
+allreduce_bulk_push_kernel(DeviceComm comm, const unsigned char* __restrict__ input, PeerPointers outputs,
+                           std::size_t bytes) {
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ __align__(8) uint64_t full[kBulkStages];
+  const std::size_t tiles = (bytes + kBulkTileBytes - 1) / kBulkTileBytes;
+  unsigned char* own_out = reinterpret_cast<unsigned char*>(outputs.ptr[comm.rank]);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kBulkStages; ++s) {
+      mbar_init(&full[s], 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+
+  // phase 1: own replica starts as a copy of the own input (generic proxy, all threads)
+  for (std::size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const std::size_t off = t * kBulkTileBytes;
+    const std::size_t len = std::min<std::size_t>(kBulkTileBytes, bytes - off);
+    const uint4* src = reinterpret_cast<const uint4*>(input + off);
+    uint4* dst = reinterpret_cast<uint4*>(own_out + off);
+    for (std::size_t v = threadIdx.x; v < len / 16; v += blockDim.x) {
+      dst[v] = src[v];
+    }
+  }
+  dev::fence_proxy_async_global();  // later bulk (async proxy) accesses must see these writes
+  if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
+    return;
+  }
+  if (comm.world == 1) {
+    return;
+  }
+
+  // phase 2: one thread drives the TMA engine: ring of tiles, loads ahead of store-reduces
+  if (threadIdx.x == 0) {
+    bool ok = true;
+    const std::size_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    auto tile_offset = [&](std::size_t k) { return (blockIdx.x + k * gridDim.x) * static_cast<std::size_t>(kBulkTileBytes); };
+    auto tile_len = [&](std::size_t k) {
+      return static_cast<uint32_t>(std::min<std::size_t>(kBulkTileBytes, bytes - tile_offset(k)));
+    };
+    auto issue_load = [&](std::size_t k) {
+      const int s = static_cast<int>(k % kBulkStages);
+      mbar_expect_tx(&full[s], tile_len(k));
+      bulk_load(ring + s * kBulkTileBytes, input + tile_offset(k), tile_len(k), &full[s]);
+    };
+    for (std::size_t k = 0; k < my_tiles && k < kBulkStages - 1; ++k) {
+      issue_load(k);
+    }
+    for (std::size_t k = 0; k < my_tiles && ok; ++k) {
+      const int s = static_cast<int>(k % kBulkStages);
+      if (!mbar_wait(&full[s], static_cast<uint32_t>((k / kBulkStages) & 1), comm.timeout_ns)) {
+        dev::report(comm, kStatusCopyTimeout, static_cast<uint32_t>(k));
+        ok = false;
+        break;
+      }
+      const std::size_t off = tile_offset(k);
+      const uint32_t len = tile_len(k);
+#if MSHARP_HAS_BULK_MULTIMEM
+      // (kept for toolchains that know the instruction; destination must then be a zeroed
+      //  multicast alias and phase 1 a zero fill: see bulk_multimem_compiled())
+#endif
+      for (int r = 1; r < comm.world; ++r) {
+        const int peer = (comm.rank + r) % comm.world;  // stagger so that peers are hit evenly
+        bulk_reduce_add<DT>(reinterpret_cast<unsigned char*>(outputs.ptr[peer]) + off, ring + s * kBulkTileBytes, len);
+      }
+      bulk_commit();
+      // The stage that tile k + STAGES - 1 will use was last read by the group of tile k - 1.
+      if (k + kBulkStages - 1 < my_tiles) {
+        bulk_wait_read<1>();  // all groups but the newest have finished reading shared memory
+        issue_load(k + kBulkStages - 1);
+      }
+    }
+    bulk_wait_all();  // every add has been performed at its destination
+  }
+  __syncthreads();
+  dev::grid_peers_barrier(comm, kStatusExitTimeout);
+}
+
+// ------------------------------------------------------------------------------------ launch helpers
+template <typename Kernel>
+int resident_grid(Kernel kernel, int block, std::size_t dynamic_smem, std::size_t work_ctas, int requested) {
+  int per_sm = 0;
+  MSHARP_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, dynamic_smem));
+  if (per_sm < 1) {
+    throw std::runtime_error("kernel does not fit on an SM with the requested block size");
+  }
+  // CTAs of different ranks wait for one another, so all of them must be resident at once.
+  const int resident = per_sm * device_sm_count();
+  int grid = requested > 0 ? requested : resident;
+  grid = std::min(grid, resident);
+  grid = std::min(grid, kMaxBarrierSlots);
+  grid = static_cast<int>(std::min<std::size_t>(static_cast<std::size_t>(grid), std::max<std::size_t>(work_ctas, 1)));
+  return std::max(grid, 1);
+}
+
+void validate_buffer(const void* p, std::size_t bytes, const char* what) {
+  if (p == nullptr) {
+    throw std::runtime_error(std::string(what) + ": null buffer");
+  }
+  if (reinterpret_cast<uintptr_t>(p) % 16 != 0) {
+    throw std::runtime_error(std::string(what) + ": buffer must be 16-byte aligned");
+  }
+  if (bytes == 0 || bytes % 4 != 0) {
+    throw std::runtime_error(std::string(what) + ": size must be a nonzero multiple of 4 bytes");
+  }
+}
+
+template <int KIND>
+void launch_pull_kind(const DeviceComm& comm, void* data, std::size_t bytes, const LaunchShape& shape,
+                      cudaStream_t stream) {
+  const std::size_t vectors = bytes / 16;
+  const std::size_t tail_words = (bytes % 16) / 4;
+  const int block = shape.block > 0 ? shape.block : 512;
+  const int unroll = shape.unroll > 0 ? shape.unroll : 4;
+  const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
+  auto go = [&](auto kernel, int u) {
+    const std::size_t work = (per_rank + static_cast<std::size_t>(block) * u - 1) / (static_cast<std::size_t>(block) * u);
+    const int grid = resident_grid(kernel, block, 0, work, shape.grid);
+    kernel<<<grid, block, 0, stream>>>(comm, static_cast<uint4*>(data), vectors, tail_words);
+  };
+  switch (unroll) {
+    case 1:
+      go(allreduce_pull_kernel<KIND, 1>, 1);
+      break;
+    case 2:
+      go(allreduce_pull_kernel<KIND, 2>, 2);
+      break;
+    case 4:
+      go(allreduce_pull_kernel<KIND, 4>, 4);
+      break;
+    case 8:
+      go(allreduce_pull_kernel<KIND, 8>, 8);
+      break;
+    default:
+      throw std::runtime_error("pull all-reduce: unroll must be 1, 2, 4 or 8");
+  }
+  check_launch("allreduce_pull_kernel");
+}
+
+int pull_kind(Dtype dtype, PullAcc acc) {
+  switch (dtype) {
+    case Dtype::kE4M3:
+      return dev::kReduceE4M3AccF16;
+    case Dtype::kF16:
+      return acc == PullAcc::kF32 ? dev::kReduceF16AccF32 : dev::kReduceF16AccF16;
+    case Dtype::kBF16:
+      return acc == PullAcc::kF32 ? dev::kReduceBF16AccF32 : dev::kReduceBF16AccBF16;
+  }
+  return dev::kReduceE4M3AccF16;
+}
+
+}  // namespace
+
+void launch_allreduce_pull(const DeviceComm& comm, Dtype dtype, PullAcc acc, void* mc_data, std::size_t bytes,
+                           const LaunchShape& shape, cudaStream_t stream) {
+  validate_buffer(mc_data, bytes, "pull all-reduce");
+  if (comm.world == 1) {
+    launch_pull_kind<dev::kReduceLocalCopy>(comm, mc_data, bytes, shape, stream);
+    return;
+  }
+  switch (pull_kind(dtype, acc)) {
+    case dev::kReduceE4M3AccF16:
+      launch_pull_kind<dev::kReduceE4M3AccF16>(comm, mc_data, bytes, shape, stream);
+      break;
+    case dev::kReduceF16AccF32:
+      launch_pull_kind<dev::kReduceF16AccF32>(comm, mc_data, bytes, shape, stream);
+      break;
+    case dev::kReduceF16AccF16:
+      launch_pull_kind<dev::kReduceF16AccF16>(comm, mc_data, bytes, shape, stream);
+      break;
+    case dev::kReduceBF16AccF32:
+      launch_pull_kind<dev::kReduceBF16AccF32>(comm, mc_data, bytes, shape, stream);
+      break;
+    default:
+      launch_pull_kind<dev::kReduceBF16AccBF16>(comm, mc_data, bytes, shape, stream);
+      break;
+  }
+}
+
+void launch_allreduce_reference_geometry(Dtype dtype, void* mc_data, std::size_t bytes, cudaStream_t stream) {
+  validate_buffer(mc_data, bytes, "reference-geometry all-reduce");
+  const std::size_t words = bytes / 4;
+  const int grid = static_cast<int>(std::min<std::size_t>(4096, std::max<std::size_t>(1, (words + 255) / 256)));
+  switch (dtype) {
+    case Dtype::kE4M3:
+      allreduce_reference_geometry_kernel<dev::kReduceE4M3AccF16><<<grid, 256, 0, stream>>>(static_cast<uint32_t*>(mc_data), words);
+      break;
+    case Dtype::kF16:
+      allreduce_reference_geometry_kernel<dev::kReduceF16AccF16><<<grid, 256, 0, stream>>>(static_cast<uint32_t*>(mc_data), words);
+      break;
+    case Dtype::kBF16:
+      allreduce_reference_geometry_kernel<dev::kReduceBF16AccBF16><<<grid, 256, 0, stream>>>(static_cast<uint32_t*>(mc_data), words);
+      break;
+  }
+  check_launch("allreduce_reference_geometry_kernel");
+}
+
+void launch_allreduce_sw_f32(const DeviceComm& comm, const PeerPointers& slots, void* mc_data, std::size_t bytes,
+                             const float* in_scales_device, float out_scale_inv, const LaunchShape& shape,
+                             cudaStream_t stream) {
+  validate_buffer(reinterpret_cast<const void*>(slots.ptr[comm.rank]), bytes, "sw_f32 all-reduce");
+  const std::size_t vectors = bytes / 16;
+  const std::size_t tail_words = (bytes % 16) / 4;
+  const int block = shape.block > 0 ? std::min(shape.block, 512) : 256;
+  const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
+  const std::size_t work = (per_rank + static_cast<std::size_t>(block) - 1) / static_cast<std::size_t>(block);
+  if (mc_data != nullptr && comm.world > 1) {
+    const int grid = resident_grid(allreduce_sw_f32_kernel<true>, block, 0, work, shape.grid);
+    allreduce_sw_f32_kernel<true><<<grid, block, 0, stream>>>(comm, slots, static_cast<uint4*>(mc_data), vectors, tail_words,
+                                                              in_scales_device, out_scale_inv);
+  } else {
+    const int grid = resident_grid(allreduce_sw_f32_kernel<false>, block, 0, work, shape.grid);
+    allreduce_sw_f32_kernel<false><<<grid, block, 0, stream>>>(comm, slots, nullptr, vectors, tail_words, in_scales_device,
+                                                               out_scale_inv);
+  }
+  check_launch("allreduce_sw_f32_kernel");
+}
+
+void launch_allreduce_bulk_push(const DeviceComm& comm, Dtype dtype, const void* local_input,
+                                const PeerPointers& outputs, std::size_t bytes, const LaunchShape& shape,
+                                cudaStream_t stream) {
+  validate_buffer(local_input, bytes, "bulk all-reduce");
+  if (bytes % 16 != 0) {
+    throw std::runtime_error("bulk all-reduce: size must be a multiple of 16 bytes");
+  }
+  if (dtype == Dtype::kE4M3) {
+    throw std::runtime_error("bulk all-reduce: the memory-side add has no FP8 form");
+  }
+  for (int r = 0; r < comm.world; ++r) {
+    if (outputs.ptr[r] == 0 || outputs.ptr[r] % 16 != 0) {
+      throw std::runtime_error("bulk all-reduce: output of rank " + std::to_string(r) + " is null or misaligned");
+    }
+  }
+  const std::size_t smem = static_cast<std::size_t>(kBulkStages) * kBulkTileBytes;
+  const std::size_t tiles = (bytes + kBulkTileBytes - 1) / kBulkTileBytes;
+  auto go = [&](auto kernel) {
+    MSHARP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    const int grid = resident_grid(kernel, kBulkThreads, smem, tiles, shape.grid);
+    kernel<<<grid, kBulkThreads, smem, stream>>>(comm, static_cast<const unsigned char*>(local_input), outputs, bytes);
+  };
+  if (dtype == Dtype::kF16) {
+    go(allreduce_bulk_push_kernel<1>);
+  } else {
+    go(allreduce_bulk_push_kernel<2>);
+  }
+  check_launch("allreduce_bulk_push_kernel");
+}
+
+bool bulk_multimem_compiled() { return MSHARP_HAS_BULK_MULTIMEM != 0; }
+
+}  // namespace msharp

@@ -1,0 +1,211 @@
+// Device-side building blocks: multimem wrappers, bounded waits, and the cross-GPU barrier
+// that opens and closes every collective kernel.
+#pragma once
+
+#include <cstdint>
+
+#include "msharp/device_comm.h"
+
+namespace msharp {
+namespace dev {
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void multimem_red_release_add_u32(uint32_t* mc, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_alias() { asm volatile("fence.proxy.alias;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
+// ---- 16-byte multimem operations on the multicast alias -------------------------------------
+struct Vec4 {
+  uint32_t x, y, z, w;
+};
+
+enum ReduceKind : int {
+  kReduceE4M3AccF16 = 0,
+  kReduceF16AccF32 = 1,
+  kReduceF16AccF16 = 2,
+  kReduceBF16AccF32 = 3,
+  kReduceBF16AccBF16 = 4,
+  kReduceLocalCopy = 5,  // world of one rank: plain 16-byte load (there is nothing to reduce)
+};
+
+template <int KIND>
+__device__ __forceinline__ Vec4 ld_reduce_v4(const void* mc) {
+  Vec4 v;
+  if constexpr (KIND == kReduceE4M3AccF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f16.v4.e4m3x4 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceF16AccF32) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceF16AccF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceBF16AccF32) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceBF16AccBF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  } else {
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  }
+  return v;
+}
+
+template <int KIND>
+__device__ __forceinline__ uint32_t ld_reduce_b32(const void* mc) {
+  uint32_t v;
+  if constexpr (KIND == kReduceE4M3AccF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f16.e4m3x4 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceF16AccF32) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.f16x2 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceF16AccF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.f16x2 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceBF16AccF32) {
+    asm volatile("multimem.ld_reduce.weak.global.add.acc::f32.bf16x2 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  } else if constexpr (KIND == kReduceBF16AccBF16) {
+    asm volatile("multimem.ld_reduce.weak.global.add.bf16x2 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  } else {
+    asm volatile("ld.global.u32 %0, [%1];" : "=r"(v) : "l"(mc) : "memory");
+  }
+  return v;
+}
+
+template <bool LOCAL>
+__device__ __forceinline__ void st_all_v4(void* mc, const Vec4& v) {
+  if constexpr (LOCAL) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  } else {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+  }
+}
+
+template <bool LOCAL>
+__device__ __forceinline__ void st_all_b32(void* mc, uint32_t v) {
+  if constexpr (LOCAL) {
+    asm volatile("st.global.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+  } else {
+    asm volatile("multimem.st.weak.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+  }
+}
+
+// ---- status -----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t* status_words(const DeviceComm& c) {
+  return reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlStatusOffset);
+}
+
+// Record a failure: bit set in word 0; first reporter also leaves block index and detail.
+__device__ __forceinline__ void report(const DeviceComm& c, uint32_t bit, uint32_t detail) {
+  uint32_t* s = status_words(c);
+  const uint32_t before = atomicOr(&s[0], bit);
+  if (before == 0) {
+    s[1] = blockIdx.x;
+    s[2] = detail;
+  }
+}
+
+// Spin until *p - target >= 0 (wrap-safe) or the deadline passes. Returns false on timeout.
+__device__ __forceinline__ bool wait_reach(const uint32_t* p, uint32_t target, unsigned long long timeout_ns) {
+  if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) {
+    return true;
+  }
+  const unsigned long long start = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (static_cast<int32_t>(ld_acquire_sys(p) - target) >= 0) {
+        return true;
+      }
+    }
+    if (global_timer_ns() - start > timeout_ns) {
+      return false;
+    }
+  }
+}
+
+// Cross-GPU barrier among the CTAs with the same blockIdx.x on every rank. All threads of the
+// CTA call it; returns false (for all threads) when a peer did not show up in time, in which
+// case the failure is recorded and the caller must not touch peer memory any more.
+//
+// Ordering: the caller's earlier global / multimem stores are made visible to all GPUs
+// (system-scope fence by every thread, then a CTA barrier) before the arrival is published;
+// after the wait, an acquire at system scope plus a CTA barrier orders later loads.
+__device__ __forceinline__ bool grid_peers_barrier(const DeviceComm& c, uint32_t failure_bit) {
+  __shared__ int s_ok;
+  if (c.world == 1) {
+    __syncthreads();
+    return true;
+  }
+  __threadfence_system();
+  __syncthreads();
+  const unsigned slot = blockIdx.x;
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlEpochOffset);
+  if (c.use_multimem_barrier) {
+    if (threadIdx.x == 0) {
+      const uint32_t epoch = epochs[slot] + 1;
+      epochs[slot] = epoch;
+      uint32_t* mine = reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlCounterOffset) + slot;
+      uint32_t* all = reinterpret_cast<uint32_t*>(c.ctrl_mc + kCtrlCounterOffset) + slot;
+      multimem_red_release_add_u32(all, 1u);
+      const bool ok = wait_reach(mine, epoch * static_cast<uint32_t>(c.world), c.timeout_ns);
+      if (!ok) {
+        report(c, failure_bit, ld_acquire_sys(mine));
+      }
+      s_ok = ok ? 1 : 0;
+    }
+  } else {
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+    }
+    __syncthreads();
+    const uint32_t epoch = epochs[slot] + 1;
+    const uint64_t* table = reinterpret_cast<const uint64_t*>(c.ctrl_local + kCtrlPeerTableOffset);
+    // publish to every peer first, then wait for every peer: no wait can delay a publication
+    for (int peer_rank = threadIdx.x; peer_rank < c.world; peer_rank += blockDim.x) {
+      unsigned char* peer = reinterpret_cast<unsigned char*>(table[peer_rank]);
+      st_release_sys(reinterpret_cast<uint32_t*>(peer + kCtrlFlagOffset) + slot * kMaxWorld + c.rank, epoch);
+    }
+    for (int peer_rank = threadIdx.x; peer_rank < c.world; peer_rank += blockDim.x) {
+      const uint32_t* mine =
+          reinterpret_cast<const uint32_t*>(c.ctrl_local + kCtrlFlagOffset) + slot * kMaxWorld + peer_rank;
+      if (!wait_reach(mine, epoch, c.timeout_ns)) {
+        report(c, failure_bit, peer_rank);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      epochs[slot] = epochs[slot] + 1;
+    }
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  __syncthreads();  // s_ok may be rewritten by the next barrier of this CTA
+  return ok;
+}
+
+}  // namespace dev
+}  // namespace msharp

@@ -1,0 +1,123 @@
+#include "msharp/comm_context.h"
+
+#include <cstring>
+#include <sstream>
+#include <stdexcept>
+#include <vector>
+
+namespace msharp {
+
+std::string describe_status(const DeviceStatus& s) {
+  if (s.bits == 0) {
+    return "ok";
+  }
+  std::ostringstream os;
+  os << "device status 0x" << std::hex << s.bits << std::dec << ":";
+  if (s.bits & kStatusEntryTimeout) {
+    os << " a peer did not reach the opening barrier in time;";
+  }
+  if (s.bits & kStatusExitTimeout) {
+    os << " a peer did not reach the closing barrier in time;";
+  }
+  if (s.bits & kStatusCopyTimeout) {
+    os << " a bulk copy did not complete in time;";
+  }
+  if (s.bits & kStatusBadArgument) {
+    os << " a device-side argument check failed;";
+  }
+  if (s.bits & kStatusFlagTimeout) {
+    os << " a tile-ready flag did not arrive in time;";
+  }
+  if (s.bits & kStatusCanaryMismatch) {
+    os << " canary mismatch (slot " << (s.detail >> 8) << ", word " << (s.detail & 0xff) << ");";
+  }
+  os << " first reported by block " << s.block << ", detail " << s.detail;
+  return os.str();
+}
+
+std::unique_ptr<CommContext> CommContext::create(const DriverApi& api, Bootstrap& comm, const SymmOptions& base,
+                                                 int wait_timeout_ms) {
+  std::unique_ptr<CommContext> ctx(new CommContext());
+  SymmOptions opt = base;
+  opt.payload_bytes = kCtrlBytes;
+  opt.layout = RegionLayout::kSingle;
+  ctx->block_ = SymmetricMemory::create(api, comm, opt);
+  SymmetricMemory& b = *ctx->block_;
+  if (b.alloc_bytes < kCtrlBytes) {
+    throw std::runtime_error("control block is smaller than its layout");
+  }
+  auto* local = reinterpret_cast<unsigned char*>(b.uc_slots[static_cast<std::size_t>(b.rank())]);
+  MSHARP_CUDA(cudaMemset(local, 0, kCtrlBytes));
+  std::vector<uint64_t> table(kMaxWorld, 0);
+  for (int r = 0; r < b.world(); ++r) {
+    table[static_cast<std::size_t>(r)] = static_cast<uint64_t>(b.uc_slots[static_cast<std::size_t>(r)]);
+  }
+  MSHARP_CUDA(cudaMemcpy(local + kCtrlPeerTableOffset, table.data(), table.size() * sizeof(uint64_t),
+                         cudaMemcpyHostToDevice));
+  MSHARP_CUDA(cudaDeviceSynchronize());
+  comm.barrier();  // nobody signals into a block that is still being zeroed
+
+  ctx->device_.rank = b.rank();
+  ctx->device_.world = b.world();
+  ctx->device_.ctrl_local = local;
+  ctx->device_.ctrl_mc = reinterpret_cast<unsigned char*>(b.mc_base);
+  ctx->device_.use_multimem_barrier = b.mc_base != 0 ? 1 : 0;
+  ctx->set_timeout_ms(wait_timeout_ms);
+  return ctx;
+}
+
+CommContext::~CommContext() { destroy(nullptr); }
+
+void CommContext::destroy(Bootstrap* comm) noexcept {
+  if (!block_) {
+    return;
+  }
+  if (comm != nullptr) {
+    try {
+      comm->barrier();
+    } catch (...) {
+    }
+  }
+  block_->destroy();
+  block_.reset();
+}
+
+void CommContext::set_multimem_barrier(bool enabled) {
+  if (enabled && !has_multicast()) {
+    throw std::runtime_error("multimem barrier needs a multicast alias of the control block");
+  }
+  device_.use_multimem_barrier = enabled ? 1 : 0;
+}
+
+void CommContext::set_timeout_ms(int ms) {
+  device_.timeout_ns = static_cast<unsigned long long>(ms < 1 ? 1 : ms) * 1000000ull;
+}
+
+DeviceStatus CommContext::read_status() const {
+  uint32_t words[3] = {0, 0, 0};
+  MSHARP_CUDA(cudaMemcpy(words, device_.ctrl_local + kCtrlStatusOffset, sizeof(words), cudaMemcpyDeviceToHost));
+  return DeviceStatus{words[0], words[1], words[2]};
+}
+
+void CommContext::clear_status() { MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlStatusOffset, 0, 64)); }
+
+void CommContext::throw_if_failed(const char* what) const {
+  const DeviceStatus s = read_status();
+  if (s.bits != 0) {
+    throw std::runtime_error(std::string(what) + ": " + describe_status(s));
+  }
+}
+
+void CommContext::reset(Bootstrap& comm) {
+  MSHARP_CUDA(cudaDeviceSynchronize());
+  comm.barrier();  // no kernel anywhere still signals
+  MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlCounterOffset, 0, kCtrlPeerTableOffset));
+  MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlEpochOffset, 0, kMaxBarrierSlots * sizeof(uint32_t)));
+  clear_status();
+  MSHARP_CUDA(cudaDeviceSynchronize());
+  comm.barrier();
+}
+
+uint64_t* CommContext::scratch_u64() const { return reinterpret_cast<uint64_t*>(device_.ctrl_local + kCtrlScratchOffset); }
+
+}  // namespace msharp

@@ -1,0 +1,94 @@
+#include "msharp/driver_api.h"
+
+#include <dlfcn.h>
+
+#include <mutex>
+
+namespace msharp {
+namespace {
+
+struct Loaded {
+  DriverApi api;
+  std::string error;
+  bool ok = false;
+};
+
+template <typename Fn>
+bool bind(void* lib, const char* name, Fn* slot, std::string* error) {
+  void* sym = dlsym(lib, name);
+  if (sym == nullptr) {
+    *error = std::string("libcuda.so.1 lacks ") + name;
+    return false;
+  }
+  *slot = reinterpret_cast<Fn>(sym);
+  return true;
+}
+
+Loaded load() {
+  Loaded out;
+  void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  if (lib == nullptr) {
+    out.error = "CUDA driver library libcuda.so.1 is not available on this machine";
+    return out;
+  }
+  DriverApi& a = out.api;
+  std::string* e = &out.error;
+  // Versioned names are the ones cuda.h maps the plain names to for this toolkit generation.
+  out.ok = bind(lib, "cuInit", &a.Init, e) && bind(lib, "cuDriverGetVersion", &a.DriverGetVersion, e) &&
+           bind(lib, "cuDeviceGet", &a.DeviceGet, e) && bind(lib, "cuDeviceGetCount", &a.DeviceGetCount, e) &&
+           bind(lib, "cuDeviceGetAttribute", &a.DeviceGetAttribute, e) &&
+           bind(lib, "cuCtxGetCurrent", &a.CtxGetCurrent, e) && bind(lib, "cuGetErrorName", &a.GetErrorName, e) &&
+           bind(lib, "cuGetErrorString", &a.GetErrorString, e) &&
+           bind(lib, "cuMemGetAllocationGranularity", &a.MemGetAllocationGranularity, e) &&
+           bind(lib, "cuMemCreate", &a.MemCreate, e) && bind(lib, "cuMemRelease", &a.MemRelease, e) &&
+           bind(lib, "cuMemExportToShareableHandle", &a.MemExportToShareableHandle, e) &&
+           bind(lib, "cuMemImportFromShareableHandle", &a.MemImportFromShareableHandle, e) &&
+           bind(lib, "cuMemAddressReserve", &a.MemAddressReserve, e) &&
+           bind(lib, "cuMemAddressFree", &a.MemAddressFree, e) && bind(lib, "cuMemMap", &a.MemMap, e) &&
+           bind(lib, "cuMemUnmap", &a.MemUnmap, e) && bind(lib, "cuMemSetAccess", &a.MemSetAccess, e) &&
+           bind(lib, "cuMulticastGetGranularity", &a.MulticastGetGranularity, e) &&
+           bind(lib, "cuMulticastCreate", &a.MulticastCreate, e) &&
+           bind(lib, "cuMulticastAddDevice", &a.MulticastAddDevice, e) &&
+           bind(lib, "cuMulticastBindMem", &a.MulticastBindMem, e) &&
+           bind(lib, "cuMulticastUnbind", &a.MulticastUnbind, e) && bind(lib, "cuMemcpyDtoH_v2", &a.MemcpyDtoH, e) &&
+           bind(lib, "cuMemcpyHtoD_v2", &a.MemcpyHtoD, e) && bind(lib, "cuModuleLoadDataEx", &a.ModuleLoadDataEx, e) &&
+           bind(lib, "cuModuleUnload", &a.ModuleUnload, e);
+  return out;
+}
+
+const Loaded& loaded() {
+  static const Loaded instance = load();
+  return instance;
+}
+
+}  // namespace
+
+bool real_driver_available() { return loaded().ok; }
+
+const DriverApi& real_driver() {
+  const Loaded& l = loaded();
+  if (!l.ok) {
+    throw std::runtime_error(l.error);
+  }
+  return l.api;
+}
+
+std::string driver_error_text(const DriverApi& api, CUresult code) {
+  const char* name = nullptr;
+  const char* text = nullptr;
+  if (api.GetErrorName != nullptr) {
+    api.GetErrorName(code, &name);
+  }
+  if (api.GetErrorString != nullptr) {
+    api.GetErrorString(code, &text);
+  }
+  return std::string(name != nullptr ? name : "CUDA_ERROR_UNKNOWN") + ": " + (text != nullptr ? text : "unknown error");
+}
+
+void check_driver(const DriverApi& api, CUresult code, const char* expression) {
+  if (code != CUDA_SUCCESS) {
+    throw std::runtime_error(std::string(expression) + " failed: " + driver_error_text(api, code));
+  }
+}
+
+}  // namespace msharp

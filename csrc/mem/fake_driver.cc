@@ -1,0 +1,486 @@
+#include "msharp/fake_driver.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <sstream>
+
+namespace msharp {
+namespace {
+
+struct Handle {
+  bool multicast = false;
+  size_t size = 0;
+  int fd = -1;
+  int device = 0;
+  std::vector<int> added_devices;
+  int bindings = 0;
+};
+
+struct Reservation {
+  void* raw = nullptr;
+  size_t raw_size = 0;
+  size_t size = 0;
+};
+
+struct Mapping {
+  size_t size = 0;
+  CUmemGenericAllocationHandle handle = 0;
+};
+
+struct State {
+  std::mutex mu;
+  int device_count = 8;
+  std::map<int, int> attributes;
+  std::map<CUmemGenericAllocationHandle, Handle> handles;
+  CUmemGenericAllocationHandle next_handle = 0x1000;
+  std::map<uintptr_t, Reservation> reservations;
+  std::map<uintptr_t, Mapping> mappings;
+  std::vector<std::string> log;
+  std::map<std::string, std::map<int, CUresult>> failures;  // name -> (call number -> code)
+  std::map<std::string, int> counts;
+};
+
+State& state() {
+  static State s;
+  return s;
+}
+
+constexpr size_t kGranularity = 2u << 20;
+
+// Log the call; returns the injected failure if one is due.
+CUresult enter(const std::string& name, const std::string& detail = "") {
+  State& s = state();
+  s.log.push_back(detail.empty() ? name : name + "(" + detail + ")");
+  const int n = ++s.counts[name];
+  auto it = s.failures.find(name);
+  if (it != s.failures.end()) {
+    auto hit = it->second.find(n);
+    if (hit != it->second.end()) {
+      const CUresult code = hit->second;
+      it->second.erase(hit);
+      return code;
+    }
+  }
+  return CUDA_SUCCESS;
+}
+
+#define FAKE_ENTER(name, detail)                        \
+  std::lock_guard<std::mutex> lock(state().mu);         \
+  if (CUresult injected = enter(name, detail); injected != CUDA_SUCCESS) return injected
+
+std::string hex(uint64_t v) {
+  std::ostringstream os;
+  os << "0x" << std::hex << v;
+  return os.str();
+}
+
+CUresult f_Init(unsigned int) {
+  FAKE_ENTER("cuInit", "");
+  return CUDA_SUCCESS;
+}
+
+CUresult f_DriverGetVersion(int* v) {
+  *v = 13000;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_DeviceGet(CUdevice* dev, int ordinal) {
+  FAKE_ENTER("cuDeviceGet", std::to_string(ordinal));
+  if (ordinal < 0 || ordinal >= state().device_count) {
+    return CUDA_ERROR_INVALID_DEVICE;
+  }
+  *dev = ordinal;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_DeviceGetCount(int* count) {
+  *count = state().device_count;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_DeviceGetAttribute(int* value, CUdevice_attribute attrib, CUdevice) {
+  FAKE_ENTER("cuDeviceGetAttribute", std::to_string(static_cast<int>(attrib)));
+  auto it = state().attributes.find(static_cast<int>(attrib));
+  *value = it == state().attributes.end() ? 0 : it->second;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_CtxGetCurrent(CUcontext* ctx) {
+  *ctx = reinterpret_cast<CUcontext>(0x1);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_GetErrorName(CUresult code, const char** name) {
+  switch (code) {
+    case CUDA_SUCCESS:
+      *name = "CUDA_SUCCESS";
+      break;
+    case CUDA_ERROR_INVALID_VALUE:
+      *name = "CUDA_ERROR_INVALID_VALUE";
+      break;
+    case CUDA_ERROR_OUT_OF_MEMORY:
+      *name = "CUDA_ERROR_OUT_OF_MEMORY";
+      break;
+    case CUDA_ERROR_NOT_SUPPORTED:
+      *name = "CUDA_ERROR_NOT_SUPPORTED";
+      break;
+    case CUDA_ERROR_NOT_PERMITTED:
+      *name = "CUDA_ERROR_NOT_PERMITTED";
+      break;
+    case CUDA_ERROR_INVALID_DEVICE:
+      *name = "CUDA_ERROR_INVALID_DEVICE";
+      break;
+    case CUDA_ERROR_INVALID_HANDLE:
+      *name = "CUDA_ERROR_INVALID_HANDLE";
+      break;
+    default:
+      *name = "CUDA_ERROR_UNKNOWN";
+  }
+  return CUDA_SUCCESS;
+}
+
+CUresult f_GetErrorString(CUresult code, const char** text) {
+  *text = code == CUDA_SUCCESS ? "no error" : "injected or simulated driver error";
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemGetAllocationGranularity(size_t* g, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) {
+  FAKE_ENTER("cuMemGetAllocationGranularity", "");
+  *g = kGranularity;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemCreate(CUmemGenericAllocationHandle* out, size_t size, const CUmemAllocationProp* prop,
+                     unsigned long long) {
+  FAKE_ENTER("cuMemCreate", "size=" + std::to_string(size) + ",type=" + std::to_string(prop->requestedHandleTypes));
+  if (size == 0 || size % kGranularity != 0) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  const int fd = memfd_create("msharp-fake", MFD_CLOEXEC);
+  if (fd < 0 || ftruncate(fd, static_cast<off_t>(size)) != 0) {
+    if (fd >= 0) {
+      close(fd);
+    }
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  Handle h;
+  h.size = size;
+  h.fd = fd;
+  h.device = prop->location.id;
+  *out = state().next_handle++;
+  state().handles[*out] = h;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemRelease(CUmemGenericAllocationHandle handle) {
+  FAKE_ENTER("cuMemRelease", hex(handle));
+  auto it = state().handles.find(handle);
+  if (it == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  close(it->second.fd);
+  state().handles.erase(it);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemExport(void* shareable, CUmemGenericAllocationHandle handle, CUmemAllocationHandleType type,
+                     unsigned long long) {
+  FAKE_ENTER("cuMemExportToShareableHandle", hex(handle) + ",type=" + std::to_string(type));
+  auto it = state().handles.find(handle);
+  if (it == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
+    return CUDA_ERROR_NOT_SUPPORTED;
+  }
+  const int dupfd = fcntl(it->second.fd, F_DUPFD_CLOEXEC, 0);
+  if (dupfd < 0) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  *static_cast<int*>(shareable) = dupfd;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemImport(CUmemGenericAllocationHandle* out, void* os_handle, CUmemAllocationHandleType type) {
+  FAKE_ENTER("cuMemImportFromShareableHandle", "type=" + std::to_string(type));
+  if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
+    return CUDA_ERROR_NOT_SUPPORTED;
+  }
+  const int fd = static_cast<int>(reinterpret_cast<intptr_t>(os_handle));
+  struct stat st;
+  if (fstat(fd, &st) != 0) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  Handle h;
+  h.size = static_cast<size_t>(st.st_size);
+  h.fd = fcntl(fd, F_DUPFD_CLOEXEC, 0);
+  if (h.fd < 0) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  *out = state().next_handle++;
+  state().handles[*out] = h;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemAddressReserve(CUdeviceptr* ptr, size_t size, size_t alignment, CUdeviceptr, unsigned long long) {
+  FAKE_ENTER("cuMemAddressReserve", "size=" + std::to_string(size));
+  if (size == 0) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  const size_t align = alignment == 0 ? kGranularity : alignment;
+  Reservation r;
+  r.size = size;
+  r.raw_size = size + align;
+  r.raw = mmap(nullptr, r.raw_size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);
+  if (r.raw == MAP_FAILED) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  const uintptr_t base = (reinterpret_cast<uintptr_t>(r.raw) + align - 1) / align * align;
+  *ptr = static_cast<CUdeviceptr>(base);
+  state().reservations[base] = r;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemAddressFree(CUdeviceptr ptr, size_t size) {
+  FAKE_ENTER("cuMemAddressFree", "size=" + std::to_string(size));
+  auto it = state().reservations.find(static_cast<uintptr_t>(ptr));
+  if (it == state().reservations.end() || it->second.size != size) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  munmap(it->second.raw, it->second.raw_size);
+  state().reservations.erase(it);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemMap(CUdeviceptr ptr, size_t size, size_t offset, CUmemGenericAllocationHandle handle,
+                  unsigned long long) {
+  FAKE_ENTER("cuMemMap", "size=" + std::to_string(size) + ",handle=" + hex(handle));
+  auto it = state().handles.find(handle);
+  if (it == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  if (offset + size > it->second.size) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  void* at = mmap(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)), size, PROT_NONE, MAP_SHARED | MAP_FIXED,
+                  it->second.fd, static_cast<off_t>(offset));
+  if (at == MAP_FAILED) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  state().mappings[static_cast<uintptr_t>(ptr)] = Mapping{size, handle};
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemUnmap(CUdeviceptr ptr, size_t size) {
+  FAKE_ENTER("cuMemUnmap", "size=" + std::to_string(size));
+  auto it = state().mappings.find(static_cast<uintptr_t>(ptr));
+  if (it == state().mappings.end() || it->second.size != size) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  mmap(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)), size, PROT_NONE,
+       MAP_PRIVATE | MAP_ANONYMOUS | MAP_FIXED | MAP_NORESERVE, -1, 0);
+  state().mappings.erase(it);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemSetAccess(CUdeviceptr ptr, size_t size, const CUmemAccessDesc*, size_t) {
+  FAKE_ENTER("cuMemSetAccess", "size=" + std::to_string(size));
+  if (mprotect(reinterpret_cast<void*>(static_cast<uintptr_t>(ptr)), size, PROT_READ | PROT_WRITE) != 0) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MulticastGetGranularity(size_t* g, const CUmulticastObjectProp*, CUmulticastGranularity_flags) {
+  FAKE_ENTER("cuMulticastGetGranularity", "");
+  *g = kGranularity;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MulticastCreate(CUmemGenericAllocationHandle* out, const CUmulticastObjectProp* prop) {
+  FAKE_ENTER("cuMulticastCreate", "devices=" + std::to_string(prop->numDevices) + ",size=" + std::to_string(prop->size));
+  if (prop->numDevices < 2 || prop->size == 0 || prop->size % kGranularity != 0) {
+    return CUDA_ERROR_INVALID_VALUE;  // the real driver also refuses single-device objects
+  }
+  const int fd = memfd_create("msharp-fake-mc", MFD_CLOEXEC);
+  if (fd < 0 || ftruncate(fd, static_cast<off_t>(prop->size)) != 0) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  Handle h;
+  h.multicast = true;
+  h.size = prop->size;
+  h.fd = fd;
+  *out = state().next_handle++;
+  state().handles[*out] = h;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MulticastAddDevice(CUmemGenericAllocationHandle handle, CUdevice dev) {
+  FAKE_ENTER("cuMulticastAddDevice", hex(handle) + ",dev=" + std::to_string(dev));
+  auto it = state().handles.find(handle);
+  if (it == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  it->second.added_devices.push_back(dev);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MulticastBindMem(CUmemGenericAllocationHandle mc, size_t mc_offset, CUmemGenericAllocationHandle mem,
+                            size_t mem_offset, size_t size, unsigned long long) {
+  FAKE_ENTER("cuMulticastBindMem", "size=" + std::to_string(size));
+  auto m = state().handles.find(mc);
+  auto h = state().handles.find(mem);
+  if (m == state().handles.end() || h == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  if (mc_offset + size > m->second.size || mem_offset + size > h->second.size || m->second.added_devices.empty()) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  ++m->second.bindings;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MulticastUnbind(CUmemGenericAllocationHandle mc, CUdevice, size_t, size_t size) {
+  FAKE_ENTER("cuMulticastUnbind", "size=" + std::to_string(size));
+  auto m = state().handles.find(mc);
+  if (m == state().handles.end()) {
+    return CUDA_ERROR_INVALID_HANDLE;
+  }
+  if (m->second.bindings <= 0) {
+    return CUDA_ERROR_INVALID_VALUE;
+  }
+  --m->second.bindings;
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemcpyDtoH(void* dst, CUdeviceptr src, size_t bytes) {
+  FAKE_ENTER("cuMemcpyDtoH", "bytes=" + std::to_string(bytes));
+  std::memcpy(dst, reinterpret_cast<const void*>(static_cast<uintptr_t>(src)), bytes);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_MemcpyHtoD(CUdeviceptr dst, const void* src, size_t bytes) {
+  FAKE_ENTER("cuMemcpyHtoD", "bytes=" + std::to_string(bytes));
+  std::memcpy(reinterpret_cast<void*>(static_cast<uintptr_t>(dst)), src, bytes);
+  return CUDA_SUCCESS;
+}
+
+CUresult f_ModuleLoadDataEx(CUmodule*, const void*, unsigned int, CUjit_option*, void**) {
+  FAKE_ENTER("cuModuleLoadDataEx", "");
+  return CUDA_ERROR_UNSUPPORTED_PTX_VERSION;
+}
+
+CUresult f_ModuleUnload(CUmodule) { return CUDA_SUCCESS; }
+
+DriverApi make_table() {
+  DriverApi a;
+  a.Init = f_Init;
+  a.DriverGetVersion = f_DriverGetVersion;
+  a.DeviceGet = f_DeviceGet;
+  a.DeviceGetCount = f_DeviceGetCount;
+  a.DeviceGetAttribute = f_DeviceGetAttribute;
+  a.CtxGetCurrent = f_CtxGetCurrent;
+  a.GetErrorName = f_GetErrorName;
+  a.GetErrorString = f_GetErrorString;
+  a.MemGetAllocationGranularity = f_MemGetAllocationGranularity;
+  a.MemCreate = f_MemCreate;
+  a.MemRelease = f_MemRelease;
+  a.MemExportToShareableHandle = f_MemExport;
+  a.MemImportFromShareableHandle = f_MemImport;
+  a.MemAddressReserve = f_MemAddressReserve;
+  a.MemAddressFree = f_MemAddressFree;
+  a.MemMap = f_MemMap;
+  a.MemUnmap = f_MemUnmap;
+  a.MemSetAccess = f_MemSetAccess;
+  a.MulticastGetGranularity = f_MulticastGetGranularity;
+  a.MulticastCreate = f_MulticastCreate;
+  a.MulticastAddDevice = f_MulticastAddDevice;
+  a.MulticastBindMem = f_MulticastBindMem;
+  a.MulticastUnbind = f_MulticastUnbind;
+  a.MemcpyDtoH = f_MemcpyDtoH;
+  a.MemcpyHtoD = f_MemcpyHtoD;
+  a.ModuleLoadDataEx = f_ModuleLoadDataEx;
+  a.ModuleUnload = f_ModuleUnload;
+  a.is_fake = true;
+  return a;
+}
+
+void default_attributes(State& s) {
+  s.attributes.clear();
+  s.attributes[CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED] = 1;
+  s.attributes[CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED] = 1;
+  s.attributes[CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED] = 0;
+  s.attributes[CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED] = 1;
+  s.attributes[CU_DEVICE_ATTRIBUTE_HOST_NUMA_ID] = 0;
+}
+
+}  // namespace
+
+const DriverApi& fake_driver() {
+  static const DriverApi table = [] {
+    default_attributes(state());
+    return make_table();
+  }();
+  return table;
+}
+
+void fake_driver_reset(int device_count) {
+  State& s = state();
+  std::lock_guard<std::mutex> lock(s.mu);
+  for (auto& m : s.mappings) {
+    munmap(reinterpret_cast<void*>(m.first), m.second.size);
+  }
+  for (auto& r : s.reservations) {
+    munmap(r.second.raw, r.second.raw_size);
+  }
+  for (auto& h : s.handles) {
+    close(h.second.fd);
+  }
+  s.mappings.clear();
+  s.reservations.clear();
+  s.handles.clear();
+  s.log.clear();
+  s.failures.clear();
+  s.counts.clear();
+  s.device_count = device_count;
+  default_attributes(s);
+}
+
+void fake_driver_set_attribute(CUdevice_attribute attribute, int value) {
+  State& s = state();
+  std::lock_guard<std::mutex> lock(s.mu);
+  s.attributes[static_cast<int>(attribute)] = value;
+}
+
+void fake_driver_fail_call(const std::string& name, int nth, CUresult code) {
+  State& s = state();
+  std::lock_guard<std::mutex> lock(s.mu);
+  s.failures[name][s.counts[name] + nth] = code;
+}
+
+std::vector<std::string> fake_driver_call_log() {
+  State& s = state();
+  std::lock_guard<std::mutex> lock(s.mu);
+  return s.log;
+}
+
+FakeDriverLeaks fake_driver_leaks() {
+  State& s = state();
+  std::lock_guard<std::mutex> lock(s.mu);
+  FakeDriverLeaks l;
+  l.handles = static_cast<int>(s.handles.size());
+  l.reservations = static_cast<int>(s.reservations.size());
+  l.mappings = static_cast<int>(s.mappings.size());
+  for (const auto& h : s.handles) {
+    l.multicast_bindings += h.second.bindings;
+  }
+  return l;
+}
+
+}  // namespace msharp

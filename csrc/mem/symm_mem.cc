@@ -1,0 +1,370 @@
+#include "msharp/symm_mem.h"
+
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+#include <functional>
+#include <limits>
+#include <stdexcept>
+
+namespace msharp {
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+CUmemAllocationProp allocation_prop(int device_ordinal, CUmemAllocationHandleType type) {
+  CUmemAllocationProp prop;
+  std::memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device_ordinal;
+  prop.requestedHandleTypes = type;
+  return prop;
+}
+
+CUmemAccessDesc read_write_for(int device_ordinal) {
+  CUmemAccessDesc desc;
+  std::memset(&desc, 0, sizeof(desc));
+  desc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  desc.location.id = device_ordinal;
+  desc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  return desc;
+}
+
+// Run `step` and make its outcome common knowledge: if it threw on any rank, every rank throws.
+void agreed(Bootstrap& comm, const char* phase, const std::function<void()>& step) {
+  std::string error;
+  try {
+    step();
+  } catch (const BootstrapError&) {
+    throw;  // the control plane itself is broken; nothing to agree over
+  } catch (const std::exception& ex) {
+    error = ex.what();
+  }
+  const bool everyone_ok = comm.all_true(error.empty());
+  if (!error.empty()) {
+    throw std::runtime_error(std::string(phase) + ": " + error);
+  }
+  if (!everyone_ok) {
+    throw std::runtime_error(std::string(phase) + ": failed on another rank");
+  }
+}
+
+}  // namespace
+
+std::size_t align_up(std::size_t value, std::size_t alignment) {
+  if (alignment == 0) {
+    throw std::runtime_error("alignment cannot be zero");
+  }
+  const std::size_t rem = value % alignment;
+  if (rem == 0) {
+    return value;
+  }
+  const std::size_t pad = alignment - rem;
+  if (value > std::numeric_limits<std::size_t>::max() - pad) {
+    throw std::runtime_error("aligned size overflows size_t");
+  }
+  return value + pad;
+}
+
+std::unique_ptr<SymmetricMemory> SymmetricMemory::create(const DriverApi& api, Bootstrap& comm,
+                                                         const SymmOptions& options) {
+  std::unique_ptr<SymmetricMemory> mem(new SymmetricMemory(api, comm.rank(), comm.world()));
+  try {
+    mem->build(comm, options);
+  } catch (...) {
+    mem->destroy();
+    throw;
+  }
+  return mem;
+}
+
+void SymmetricMemory::build(Bootstrap& comm, const SymmOptions& opt) {
+  if (opt.payload_bytes == 0) {
+    throw std::runtime_error("symmetric allocation needs a nonzero payload");
+  }
+  device_ = opt.cu_device;
+  payload_bytes = opt.payload_bytes;
+  const bool solo = world_ == 1;
+
+  // ---- which handle type
+  CUmemAllocationHandleType handle_type = CU_MEM_HANDLE_TYPE_NONE;
+  if (!solo) {
+    const bool want_fabric = opt.handle_type == HandleChoice::kFabric ||
+                             (opt.handle_type == HandleChoice::kAuto && !opt.posix_fd_supported && opt.fabric_supported);
+    if (want_fabric) {
+      if (!opt.fabric_supported) {
+        throw std::runtime_error("fabric handles were requested but this GPU does not support them");
+      }
+      handle_type = CU_MEM_HANDLE_TYPE_FABRIC;
+      handle_kind = "fabric";
+    } else {
+      if (!opt.posix_fd_supported) {
+        throw std::runtime_error("POSIX file-descriptor handles are not supported by this GPU");
+      }
+      handle_type = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+      handle_kind = "posix_fd";
+    }
+  } else {
+    handle_kind = "none";
+  }
+  const bool use_multicast = !solo && opt.want_multicast && opt.multicast_supported;
+
+  // ---- sizes
+  const CUmemAllocationProp prop = allocation_prop(opt.device_ordinal, handle_type);
+  MSHARP_CU(api_, MemGetAllocationGranularity(&vmm_granularity, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
+  std::size_t granularity = vmm_granularity;
+  CUmulticastObjectProp mc_prop;
+  std::memset(&mc_prop, 0, sizeof(mc_prop));
+  if (use_multicast) {
+    mc_prop.numDevices = static_cast<unsigned int>(world_);
+    mc_prop.size = align_up(payload_bytes, vmm_granularity);
+    mc_prop.handleTypes = handle_type;
+    MSHARP_CU(api_, MulticastGetGranularity(&multicast_granularity, &mc_prop, CU_MULTICAST_GRANULARITY_MINIMUM));
+    granularity = std::max(granularity, multicast_granularity);
+  }
+  const std::size_t region = align_up(payload_bytes, granularity);
+  if (opt.layout == RegionLayout::kSingle) {
+    input_offset = output_offset = multicast_bind_offset = 0;
+    alloc_bytes = region;
+  } else {
+    input_offset = 0;
+    output_offset = multicast_bind_offset = region;
+    if (region > std::numeric_limits<std::size_t>::max() - region) {
+      throw std::runtime_error("allocation size overflows size_t");
+    }
+    alloc_bytes = region * 2;
+  }
+  multicast_bytes = use_multicast ? region : 0;
+
+  MSHARP_CU(api_, MemCreate(&local_handle_, alloc_bytes, &prop, 0));
+
+  imported_.assign(static_cast<std::size_t>(world_), 0);
+  slot_mapped_.assign(static_cast<std::size_t>(world_), false);
+  uc_slots.assign(static_cast<std::size_t>(world_), 0);
+
+  // ---- timed phase: export, exchange, import, reserve, map
+  comm.barrier();
+  const auto t0 = Clock::now();
+  agreed(comm, "peer mapping", [&] {
+    if (!solo && handle_type == CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
+      int fd = -1;
+      std::string first_error;
+      const CUresult export_rc = api_.MemExportToShareableHandle(&fd, local_handle_, handle_type, 0);
+      if (export_rc != CUDA_SUCCESS) {
+        fd = -1;  // still take part in the exchange so that the others are not left waiting
+        first_error = "cuMemExportToShareableHandle failed: " + driver_error_text(api_, export_rc);
+      }
+      std::vector<int> fds;
+      try {
+        fds = comm.allgather_fd(fd);
+      } catch (...) {
+        if (fd >= 0) {
+          ::close(fd);
+        }
+        throw;
+      }
+      if (fd >= 0) {
+        ::close(fd);
+      }
+      for (int r = 0; r < world_; ++r) {
+        const int peer_fd = fds[static_cast<std::size_t>(r)];
+        if (r != rank_ && first_error.empty()) {
+          if (peer_fd < 0) {
+            first_error = "rank " + std::to_string(r) + " shared no handle";
+          } else {
+            const CUresult rc = api_.MemImportFromShareableHandle(
+                &imported_[static_cast<std::size_t>(r)], reinterpret_cast<void*>(static_cast<intptr_t>(peer_fd)),
+                handle_type);
+            if (rc != CUDA_SUCCESS) {
+              imported_[static_cast<std::size_t>(r)] = 0;
+              first_error = "cuMemImportFromShareableHandle(rank " + std::to_string(r) +
+                            ") failed: " + driver_error_text(api_, rc);
+            }
+          }
+        }
+        if (peer_fd >= 0) {
+          ::close(peer_fd);  // the driver keeps its own reference
+        }
+      }
+      if (!first_error.empty()) {
+        throw std::runtime_error(first_error);
+      }
+    } else if (!solo) {
+      CUmemFabricHandle mine;
+      std::memset(&mine, 0, sizeof(mine));
+      MSHARP_CU(api_, MemExportToShareableHandle(&mine, local_handle_, handle_type, 0));
+      std::vector<CUmemFabricHandle> all(static_cast<std::size_t>(world_));
+      comm.allgather(&mine, all.data(), sizeof(mine));
+      for (int r = 0; r < world_; ++r) {
+        if (r != rank_) {
+          MSHARP_CU(api_, MemImportFromShareableHandle(&imported_[static_cast<std::size_t>(r)],
+                                                       &all[static_cast<std::size_t>(r)], handle_type));
+        }
+      }
+    }
+    if (alloc_bytes > std::numeric_limits<std::size_t>::max() / static_cast<std::size_t>(world_)) {
+      throw std::runtime_error("unicast address range overflows size_t");
+    }
+    uc_reserved_bytes_ = alloc_bytes * static_cast<std::size_t>(world_);
+    MSHARP_CU(api_, MemAddressReserve(&uc_base, uc_reserved_bytes_, granularity, 0, 0));
+    const CUmemAccessDesc access = read_write_for(opt.device_ordinal);
+    for (int r = 0; r < world_; ++r) {
+      const CUdeviceptr at = uc_base + static_cast<CUdeviceptr>(alloc_bytes) * static_cast<CUdeviceptr>(r);
+      const CUmemGenericAllocationHandle h = r == rank_ ? local_handle_ : imported_[static_cast<std::size_t>(r)];
+      MSHARP_CU(api_, MemMap(at, alloc_bytes, 0, h, 0));
+      slot_mapped_[static_cast<std::size_t>(r)] = true;
+      MSHARP_CU(api_, MemSetAccess(at, alloc_bytes, &access, 1));
+      uc_slots[static_cast<std::size_t>(r)] = at;
+    }
+  });
+  peer_init_local_ms = std::chrono::duration<double, std::milli>(Clock::now() - t0).count();
+  peer_init_all_ms = comm.allgather_double(peer_init_local_ms);
+
+  if (!use_multicast) {
+    return;
+  }
+
+  // ---- multicast object: created by rank 0, shared, every device added before any bind
+  agreed(comm, "multicast create", [&] {
+    if (handle_type == CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
+      int fd = -1;
+      std::string error;
+      if (rank_ == 0) {
+        mc_prop.size = multicast_bytes;
+        const CUresult rc = api_.MulticastCreate(&multicast_handle_, &mc_prop);
+        if (rc != CUDA_SUCCESS) {
+          multicast_handle_ = 0;
+          error = "cuMulticastCreate failed: " + driver_error_text(api_, rc);
+        } else {
+          const CUresult ex = api_.MemExportToShareableHandle(&fd, multicast_handle_, handle_type, 0);
+          if (ex != CUDA_SUCCESS) {
+            fd = -1;
+            error = "export of the multicast handle failed: " + driver_error_text(api_, ex);
+          }
+        }
+      }
+      const int got = comm.broadcast_fd(fd, 0);  // -1 tells the others that rank 0 failed
+      if (fd >= 0) {
+        ::close(fd);
+      }
+      if (rank_ != 0) {
+        if (got < 0) {
+          throw std::runtime_error("rank 0 could not create the multicast object");
+        }
+        const CUresult rc = api_.MemImportFromShareableHandle(
+            &multicast_handle_, reinterpret_cast<void*>(static_cast<intptr_t>(got)), handle_type);
+        ::close(got);
+        if (rc != CUDA_SUCCESS) {
+          multicast_handle_ = 0;
+          throw std::runtime_error("import of the multicast handle failed: " + driver_error_text(api_, rc));
+        }
+      } else {
+        if (got >= 0) {
+          ::close(got);
+        }
+        if (!error.empty()) {
+          throw std::runtime_error(error);
+        }
+      }
+    } else {
+      CUmemFabricHandle blob;
+      std::memset(&blob, 0, sizeof(blob));
+      int ok = 1;
+      std::string error;
+      if (rank_ == 0) {
+        mc_prop.size = multicast_bytes;
+        CUresult rc = api_.MulticastCreate(&multicast_handle_, &mc_prop);
+        if (rc == CUDA_SUCCESS) {
+          rc = api_.MemExportToShareableHandle(&blob, multicast_handle_, handle_type, 0);
+        } else {
+          multicast_handle_ = 0;
+        }
+        if (rc != CUDA_SUCCESS) {
+          ok = 0;
+          error = "multicast create/export failed: " + driver_error_text(api_, rc);
+        }
+      }
+      ok = comm.broadcast_int(ok, 0);
+      comm.broadcast(&blob, sizeof(blob), 0);
+      if (!ok) {
+        throw std::runtime_error(rank_ == 0 ? error : "rank 0 could not create the multicast object");
+      }
+      if (rank_ != 0) {
+        MSHARP_CU(api_, MemImportFromShareableHandle(&multicast_handle_, &blob, handle_type));
+      }
+    }
+  });
+  agreed(comm, "multicast add device", [&] { MSHARP_CU(api_, MulticastAddDevice(multicast_handle_, device_)); });
+  agreed(comm, "multicast bind", [&] {
+    MSHARP_CU(api_, MulticastBindMem(multicast_handle_, 0, local_handle_, multicast_bind_offset, multicast_bytes, 0));
+    multicast_bound = true;
+  });
+  agreed(comm, "multicast map", [&] {
+    MSHARP_CU(api_, MemAddressReserve(&mc_base, multicast_bytes, granularity, 0, 0));
+    MSHARP_CU(api_, MemMap(mc_base, multicast_bytes, 0, multicast_handle_, 0));
+    mc_mapped_ = true;
+    const CUmemAccessDesc access = read_write_for(opt.device_ordinal);
+    MSHARP_CU(api_, MemSetAccess(mc_base, multicast_bytes, &access, 1));
+  });
+}
+
+void SymmetricMemory::destroy() noexcept {
+  // Order: multicast alias, unbind, unicast slots, imported handles, multicast handle, own handle.
+  if (mc_base != 0) {
+    if (mc_mapped_) {
+      api_.MemUnmap(mc_base, multicast_bytes);
+      mc_mapped_ = false;
+    }
+    api_.MemAddressFree(mc_base, multicast_bytes);
+    mc_base = 0;
+  }
+  if (multicast_bound) {
+    api_.MulticastUnbind(multicast_handle_, device_, 0, multicast_bytes);
+    multicast_bound = false;
+  }
+  if (uc_base != 0) {
+    for (std::size_t r = 0; r < slot_mapped_.size(); ++r) {
+      if (slot_mapped_[r]) {
+        api_.MemUnmap(uc_base + static_cast<CUdeviceptr>(alloc_bytes) * static_cast<CUdeviceptr>(r), alloc_bytes);
+        slot_mapped_[r] = false;
+      }
+    }
+    api_.MemAddressFree(uc_base, uc_reserved_bytes_);
+    uc_base = 0;
+  }
+  uc_slots.clear();
+  for (auto& h : imported_) {
+    if (h != 0) {
+      api_.MemRelease(h);
+      h = 0;
+    }
+  }
+  if (multicast_handle_ != 0) {
+    api_.MemRelease(multicast_handle_);
+    multicast_handle_ = 0;
+  }
+  if (local_handle_ != 0) {
+    api_.MemRelease(local_handle_);
+    local_handle_ = 0;
+  }
+}
+
+SymmetricMemory::~SymmetricMemory() { destroy(); }
+
+void SymmetricMemory::copy_to_host(void* dst, int slot_rank, std::size_t offset, std::size_t bytes) const {
+  if (slot_rank < 0 || slot_rank >= world_ || offset + bytes > alloc_bytes) {
+    throw std::runtime_error("copy_to_host: range is outside the slot");
+  }
+  MSHARP_CU(api_, MemcpyDtoH(dst, uc_slots[static_cast<std::size_t>(slot_rank)] + offset, bytes));
+}
+
+void SymmetricMemory::copy_from_host(int slot_rank, std::size_t offset, const void* src, std::size_t bytes) const {
+  if (slot_rank < 0 || slot_rank >= world_ || offset + bytes > alloc_bytes) {
+    throw std::runtime_error("copy_from_host: range is outside the slot");
+  }
+  MSHARP_CU(api_, MemcpyHtoD(uc_slots[static_cast<std::size_t>(slot_rank)] + offset, src, bytes));
+}
+
+}  // namespace msharp

@@ -1,0 +1,321 @@
+#include "msharp/topology.h"
+
+#include <sched.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cerrno>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <set>
+#include <sstream>
+#include <stdexcept>
+
+#include "msharp/json.h"
+
+namespace msharp {
+
+std::string os_hostname() {
+  char buf[256] = {0};
+  if (gethostname(buf, sizeof(buf) - 1) != 0) {
+    throw std::runtime_error(std::string("gethostname failed: ") + std::strerror(errno));
+  }
+  return buf;
+}
+
+RankInfo discover_rank_info(int world_rank, int world_size, const RackConfig& rack, const RankPlan& plan,
+                            const std::string& host_label_override) {
+  if (world_size != plan.size()) {
+    throw std::runtime_error("launch world_size " + std::to_string(world_size) + " does not match selected rank_count " +
+                             std::to_string(plan.size()));
+  }
+  RankInfo info;
+  info.world_rank = world_rank;
+  info.world_size = world_size;
+  info.rack_count = static_cast<int>(rack.entries().size());
+  info.os_hostname = os_hostname();
+
+  const RankTarget& target = plan.target(world_rank);
+  const std::string match = host_label_override.empty() ? info.os_hostname : host_label_override;
+  int tray = rack.index_of_host_label(match);
+  if (tray < 0 && host_label_override.empty() && normalize_host_label(target.host_label) == "localhost") {
+    tray = target.rack_index;  // "localhost" stands for whatever machine this is
+  }
+  if (tray < 0) {
+    throw std::runtime_error("hostname '" + info.os_hostname +
+                             "' did not match rack.yaml; set MNNVL_HOST_LABEL to the rack key if the container hostname differs");
+  }
+  const RackEntry& entry = rack.entries()[static_cast<std::size_t>(tray)];
+  if (normalize_host_label(entry.host_label) != normalize_host_label(target.host_label)) {
+    throw std::runtime_error("rank " + std::to_string(world_rank) + " is running on host '" + entry.host_label +
+                             "' but the selected rank plan expects '" + target.host_label + "'");
+  }
+  info.rack_index = tray;
+  info.host_label = entry.host_label;
+  info.control_hostname = entry.control_hostname;
+  info.ssh_port = entry.ssh_port;
+  info.local_rank = plan.local_rank(world_rank);
+  info.local_size = plan.slot_count_for_host(entry.host_label);
+  info.gpu_ordinal = target.gpu_ordinal;
+  return info;
+}
+
+namespace {
+
+int attribute(const DriverApi& api, CUdevice dev, CUdevice_attribute attr) {
+  int value = 0;
+  MSHARP_CU(api, DeviceGetAttribute(&value, attr, dev));
+  return value;
+}
+
+}  // namespace
+
+bool probe_bulk_multimem(const DriverApi& api, std::string* detail) {
+  // The smallest module that contains the instruction. The offline assembler of this toolkit
+  // generation (PTX ISA 8.8) does not know it, so the question is put to the driver's own
+  // assembler, which may be newer. Nothing is launched.
+  static const char kPtx[] =
+      ".version 9.1\n.target sm_100a\n.address_size 64\n"
+      ".visible .entry msharp_bulk_probe(.param .u64 dst, .param .u32 bytes)\n{\n"
+      "  .reg .b64 %rd<3>;\n  .reg .b32 %r<3>;\n"
+      "  .shared .align 128 .b8 tile[4096];\n"
+      "  ld.param.u64 %rd1, [dst];\n  ld.param.u32 %r1, [bytes];\n"
+      "  cvta.to.global.u64 %rd2, %rd1;\n  mov.u32 %r2, tile;\n"
+      "  multimem.cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%rd2], [%r2], %r1;\n"
+      "  cp.async.bulk.commit_group;\n  cp.async.bulk.wait_group 0;\n  ret;\n}\n";
+  char error_log[1024] = {0};
+  CUjit_option options[] = {CU_JIT_ERROR_LOG_BUFFER, CU_JIT_ERROR_LOG_BUFFER_SIZE_BYTES};
+  void* values[] = {error_log, reinterpret_cast<void*>(static_cast<uintptr_t>(sizeof(error_log)))};
+  CUmodule module = nullptr;
+  const CUresult rc = api.ModuleLoadDataEx(&module, kPtx, 2, options, values);
+  if (rc == CUDA_SUCCESS) {
+    api.ModuleUnload(module);
+    if (detail != nullptr) {
+      *detail = "driver assembled PTX 9.1 multimem.cp.reduce.async.bulk";
+    }
+    return true;
+  }
+  if (detail != nullptr) {
+    std::string first_line(error_log);
+    first_line = first_line.substr(0, first_line.find('\n'));
+    *detail = driver_error_text(api, rc) + (first_line.empty() ? "" : " (" + first_line + ")");
+  }
+  return false;
+}
+
+CapabilityInfo query_capabilities(const DriverApi& api, RankInfo* rank) {
+  if (rank == nullptr) {
+    throw std::runtime_error("query_capabilities received null RankInfo");
+  }
+  MSHARP_CU(api, Init(0));
+  MSHARP_CU(api, DeviceGet(&rank->cu_device, rank->gpu_ordinal));
+  CUcontext ctx = nullptr;
+  MSHARP_CU(api, CtxGetCurrent(&ctx));
+  if (ctx == nullptr) {
+    throw std::runtime_error("no current CUDA context: make the device current before querying capabilities");
+  }
+  CapabilityInfo caps;
+  api.DriverGetVersion(&caps.driver_version);
+  const CUdevice dev = rank->cu_device;
+  caps.vmm_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED) != 0;
+  caps.posix_fd_handle_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED) != 0;
+  caps.fabric_handle_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED) != 0;
+  caps.multicast_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED) != 0;
+  rank->host_numa_id = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HOST_NUMA_ID);
+  // The FP8 multimem forms are compiled in unconditionally (sm_100a only build).
+  caps.sharp_e4m3_supported = caps.multicast_supported;
+  caps.bulk_multimem_supported = caps.multicast_supported && probe_bulk_multimem(api, nullptr);
+  // The bulk-async backend always has its unicast fan-out form, which needs peer mappings only.
+  caps.sharp_tma_async_supported = caps.vmm_supported;
+  return caps;
+}
+
+std::vector<RankMappingRecord> gather_rank_mappings(Bootstrap& comm, const RankInfo& rank) {
+  RankMappingRecord mine;
+  mine.world_rank = rank.world_rank;
+  mine.local_rank = rank.local_rank;
+  mine.rack_index = rank.rack_index;
+  mine.gpu_ordinal = rank.gpu_ordinal;
+  mine.host_numa_id = rank.host_numa_id;
+  std::snprintf(mine.host_label, sizeof(mine.host_label), "%s", rank.host_label.c_str());
+  std::snprintf(mine.os_hostname, sizeof(mine.os_hostname), "%s", rank.os_hostname.c_str());
+  std::vector<RankMappingRecord> all(static_cast<std::size_t>(comm.world()));
+  comm.allgather(&mine, all.data(), sizeof(mine));
+  std::sort(all.begin(), all.end(),
+            [](const RankMappingRecord& a, const RankMappingRecord& b) { return a.world_rank < b.world_rank; });
+  return all;
+}
+
+void validate_rank_mappings(const std::vector<RankMappingRecord>& records, const RackConfig& rack,
+                            const RankPlan& plan) {
+  if (records.size() != static_cast<std::size_t>(plan.size())) {
+    throw std::runtime_error("rank mapping record count does not match selected rank plan");
+  }
+  std::set<int> seen;
+  std::map<std::string, std::vector<const RankMappingRecord*>> by_host;
+  for (const auto& rec : records) {
+    if (!seen.insert(rec.world_rank).second) {
+      throw std::runtime_error("duplicate world rank in mapping records");
+    }
+    const std::string who = "rank " + std::to_string(rec.world_rank);
+    const RankTarget& target = plan.target(rec.world_rank);
+    by_host[normalize_host_label(rec.host_label)].push_back(&rec);
+    if (normalize_host_label(rec.host_label) != normalize_host_label(target.host_label)) {
+      throw std::runtime_error(who + " host does not match selected rank plan");
+    }
+    if (rec.rack_index != target.rack_index) {
+      throw std::runtime_error(who + " rack index does not match selected rank plan");
+    }
+    if (rec.gpu_ordinal != target.gpu_ordinal) {
+      throw std::runtime_error(who + " GPU ordinal does not match selected rank plan");
+    }
+    if (rec.host_numa_id < 0) {
+      throw std::runtime_error(who + " did not resolve a valid HOST_NUMA_ID");
+    }
+  }
+  const auto wanted_devices = plan.devices_by_host();
+  for (const auto& entry : rack.entries()) {
+    const std::string host = normalize_host_label(entry.host_label);
+    const int expected = plan.slot_count_for_host(entry.host_label);
+    const auto it = by_host.find(host);
+    const std::size_t have = it == by_host.end() ? 0 : it->second.size();
+    if (expected == 0) {
+      if (have != 0) {
+        throw std::runtime_error("rack entry " + entry.host_label + " has launched ranks but is not in the selected plan");
+      }
+      continue;
+    }
+    if (have != static_cast<std::size_t>(expected)) {
+      throw std::runtime_error("rack entry " + entry.host_label + " has " + std::to_string(have) +
+                               " launched ranks but selected rank plan expects " + std::to_string(expected));
+    }
+    std::set<int> got;
+    for (const auto* rec : it->second) {
+      got.insert(rec->gpu_ordinal);
+    }
+    const auto& want_list = wanted_devices.at(host);
+    if (got != std::set<int>(want_list.begin(), want_list.end())) {
+      throw std::runtime_error("rack entry " + entry.host_label + " launched ranks did not map to selected GPUs");
+    }
+  }
+}
+
+void validate_capabilities(Bootstrap& comm, const CapabilityInfo& caps, Backend backend, int world_size) {
+  bool backend_ok = false;
+  switch (backend) {
+    case Backend::kLegacy:
+    case Backend::kPull:
+      backend_ok = caps.sharp_e4m3_supported || world_size == 1;
+      break;
+    case Backend::kTmaAsync:
+      backend_ok = caps.sharp_tma_async_supported;
+      break;
+    case Backend::kSwF32:
+      backend_ok = caps.vmm_supported;
+      break;
+  }
+  // A single rank needs no multicast object (the driver refuses to create one for one device).
+  const bool multicast_ok = caps.multicast_supported || world_size == 1 || backend == Backend::kSwF32 ||
+                            backend == Backend::kTmaAsync;
+  const bool handle_ok = caps.posix_fd_handle_supported || caps.fabric_handle_supported || world_size == 1;
+  const bool local_ok = caps.vmm_supported && handle_ok && multicast_ok && backend_ok;
+  if (!comm.all_true(local_ok)) {
+    throw std::runtime_error(std::string("one or more selected GPUs lack VMM, a shareable handle type, multicast, or ") +
+                             to_string(backend) + " SHARP support");
+  }
+}
+
+std::vector<int> parse_cpu_list(const std::string& text) {
+  std::vector<int> cpus;
+  std::string token;
+  auto flush = [&]() {
+    // trim blanks
+    const auto b = token.find_first_not_of(" \t\r\n");
+    if (b == std::string::npos) {
+      token.clear();
+      return;
+    }
+    const auto e = token.find_last_not_of(" \t\r\n");
+    const std::string t = token.substr(b, e - b + 1);
+    token.clear();
+    const auto dash = t.find('-');
+    try {
+      if (dash == std::string::npos) {
+        cpus.push_back(std::stoi(t));
+      } else {
+        const int first = std::stoi(t.substr(0, dash));
+        const int last = std::stoi(t.substr(dash + 1));
+        if (last < first) {
+          throw std::runtime_error("invalid CPU range in cpulist: " + t);
+        }
+        for (int c = first; c <= last; ++c) {
+          cpus.push_back(c);
+        }
+      }
+    } catch (const std::invalid_argument&) {
+      throw std::runtime_error("invalid token in cpulist: " + t);
+    } catch (const std::out_of_range&) {
+      throw std::runtime_error("invalid token in cpulist: " + t);
+    }
+  };
+  for (const char c : text) {
+    if (c == ',' || c == '\n') {
+      flush();
+    } else {
+      token += c;
+    }
+  }
+  flush();
+  return cpus;
+}
+
+void pin_thread_to_numa(int numa_id) {
+  if (numa_id < 0) {
+    throw std::runtime_error("cannot pin CPU affinity because HOST_NUMA_ID is unavailable");
+  }
+  const std::string path = "/sys/devices/system/node/node" + std::to_string(numa_id) + "/cpulist";
+  std::ifstream in(path);
+  if (!in) {
+    throw std::runtime_error("could not read " + path);
+  }
+  std::stringstream buf;
+  buf << in.rdbuf();
+  const std::vector<int> cpus = parse_cpu_list(buf.str());
+  if (cpus.empty()) {
+    throw std::runtime_error("NUMA cpulist is empty for node " + std::to_string(numa_id));
+  }
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  for (int cpu : cpus) {
+    if (cpu >= 0 && cpu < CPU_SETSIZE) {
+      CPU_SET(cpu, &set);
+    }
+  }
+  if (sched_setaffinity(0, sizeof(set), &set) != 0) {
+    throw std::runtime_error("sched_setaffinity failed for NUMA node " + std::to_string(numa_id) + ": " +
+                             std::strerror(errno));
+  }
+}
+
+std::string host_mapping_json(const std::vector<RankMappingRecord>& records) {
+  JsonWriter w;
+  w.begin_array();
+  for (const auto& r : records) {
+    w.begin_object();
+    w.key("rank").value(r.world_rank);
+    w.key("local_rank").value(r.local_rank);
+    w.key("rack_index").value(r.rack_index);
+    w.key("host_label").value(r.host_label);
+    w.key("os_hostname").value(r.os_hostname);
+    w.key("gpu").value(r.gpu_ordinal);
+    w.key("host_numa_id").value(r.host_numa_id);
+    w.end_object();
+  }
+  w.end_array();
+  return w.str();
+}
+
+}  // namespace msharp
