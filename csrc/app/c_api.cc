@@ -1,0 +1,670 @@
+#include "msharp/c_api.h"
+
+#include <cuda_runtime_api.h>
+
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "msharp/bootstrap.h"
+#include "msharp/comm_context.h"
+#include "msharp/config.h"
+#include "msharp/fake_driver.h"
+#include "msharp/json.h"
+#include "msharp/kernels.h"
+#include "msharp/oracle.h"
+#include "msharp/rack.h"
+#include "msharp/report.h"
+#include "msharp/runner.h"
+#include "msharp/symm_mem.h"
+#include "msharp/topology.h"
+#include "msharp/yaml_lite.h"
+
+namespace {
+
+thread_local std::string g_error;
+thread_local std::string g_text;
+
+int guarded(const std::function<void()>& body) {
+  try {
+    body();
+    g_error.clear();
+    return 0;
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return 1;
+  }
+}
+
+const char* guarded_text(const std::function<std::string()>& body) {
+  try {
+    g_text = body();
+    g_error.clear();
+    return g_text.c_str();
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return nullptr;
+  }
+}
+
+msharp::Dtype to_dtype(int dtype) {
+  if (dtype < 0 || dtype > 2) {
+    throw std::invalid_argument("dtype must be 0 (e4m3), 1 (f16) or 2 (bf16)");
+  }
+  return static_cast<msharp::Dtype>(dtype);
+}
+
+msharp::InputSpec spec_of(int pattern, uint64_t seed, int ranks) {
+  if (pattern < 0 || pattern > 2) {
+    throw std::invalid_argument("pattern must be 0 (reference), 1 (seeded) or 2 (tagged)");
+  }
+  if (ranks < 1) {
+    throw std::invalid_argument("ranks must be >= 1");
+  }
+  msharp::InputSpec s;
+  s.pattern = pattern;
+  s.seed = seed;
+  s.ranks = ranks;
+  return s;
+}
+
+void yaml_to_json(const msharp::YamlNode& n, msharp::JsonWriter& w) {
+  switch (n.kind) {
+    case msharp::YamlNode::kNull:
+      w.null();
+      break;
+    case msharp::YamlNode::kScalar:
+      w.value(n.scalar);
+      break;
+    case msharp::YamlNode::kSequence:
+      w.begin_array();
+      for (const auto& item : n.items) {
+        yaml_to_json(item, w);
+      }
+      w.end_array();
+      break;
+    case msharp::YamlNode::kMapping:
+      w.begin_object();
+      for (const auto& e : n.entries) {
+        w.key(e.first);
+        yaml_to_json(e.second, w);
+      }
+      w.end_object();
+      break;
+  }
+}
+
+struct CommHandle {
+  msharp::Bootstrap* bootstrap = nullptr;
+  const msharp::DriverApi* api = nullptr;
+  msharp::RankInfo rank;
+  msharp::CapabilityInfo caps;
+  msharp::SymmOptions base;
+  std::unique_ptr<msharp::CommContext> ctx;
+};
+
+struct SymmHandle {
+  CommHandle* comm = nullptr;
+  std::unique_ptr<msharp::SymmetricMemory> mem;
+};
+
+cudaStream_t as_stream(uint64_t s) { return reinterpret_cast<cudaStream_t>(static_cast<uintptr_t>(s)); }
+
+msharp::PeerPointers outputs_of(const msharp::SymmetricMemory& m, std::size_t offset) {
+  msharp::PeerPointers p{};
+  for (int r = 0; r < m.world(); ++r) {
+    p.ptr[r] = static_cast<uint64_t>(m.output_ptr(r)) + offset;
+  }
+  return p;
+}
+
+void check_range(const msharp::SymmetricMemory& m, std::size_t offset, std::size_t bytes) {
+  if (offset % 16 != 0 || bytes == 0 || offset + bytes > m.payload_bytes) {
+    throw std::invalid_argument("range must start on a 16-byte boundary and lie inside the payload");
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* msharp_last_error(void) { return g_error.c_str(); }
+const char* msharp_version(void) { return "0.1.0"; }
+
+int msharp_encode(int dtype, const float* in, void* out, size_t n) {
+  return guarded([&] { msharp::cast_from_f32(to_dtype(dtype), in, n, out); });
+}
+
+int msharp_decode(int dtype, const void* in, float* out, size_t n) {
+  return guarded([&] { msharp::cast_to_f32(to_dtype(dtype), in, n, out); });
+}
+
+int msharp_generate(int dtype, int pattern, uint64_t seed, int rank, size_t first, size_t n, void* out) {
+  return guarded([&] { msharp::generate_input(to_dtype(dtype), spec_of(pattern, seed, 1), rank, first, n, out); });
+}
+
+int msharp_reduce_f32(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, float* out) {
+  return guarded([&] { msharp::reduce_f32(to_dtype(dtype), spec_of(pattern, seed, ranks), first, n, out); });
+}
+
+int msharp_reduce_f32_cast(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, void* out) {
+  return guarded([&] { msharp::reduce_f32_cast(to_dtype(dtype), spec_of(pattern, seed, ranks), first, n, out); });
+}
+
+int msharp_reduce_semantic(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, void* out) {
+  return guarded([&] { msharp::reduce_semantic(to_dtype(dtype), spec_of(pattern, seed, ranks), first, n, out); });
+}
+
+int msharp_reduce_arrays_f32(int dtype, const void* const* inputs, int ranks, size_t n, float* out) {
+  return guarded([&] { msharp::reduce_arrays_f32(to_dtype(dtype), inputs, ranks, n, out); });
+}
+
+int msharp_compare(int dtype, int pattern, uint64_t seed, int ranks, const void* result, size_t n, double* metrics) {
+  return guarded([&] {
+    const msharp::PrecisionMetrics m = msharp::compare(to_dtype(dtype), spec_of(pattern, seed, ranks), result, n);
+    metrics[0] = static_cast<double>(m.exact_mismatches);
+    metrics[1] = static_cast<double>(m.requantized_mismatches);
+    metrics[2] = static_cast<double>(m.max_requantized_ulp_distance);
+    metrics[3] = static_cast<double>(m.max_abs_error);
+    metrics[4] = m.mean_abs_error;
+    metrics[5] = static_cast<double>(m.switch_model_mismatches);
+  });
+}
+
+uint64_t msharp_hash_words(const uint32_t* words, size_t word_count) { return msharp::hash_words(words, word_count); }
+
+int msharp_summarize(const double* values, size_t n, double* out) {
+  return guarded([&] {
+    const msharp::TimingStats s = msharp::summarize(std::vector<double>(values, values + n));
+    out[0] = s.min;
+    out[1] = s.median;
+    out[2] = s.p95;
+    out[3] = s.max;
+  });
+}
+
+const char* msharp_usage(const char* argv0) {
+  return guarded_text([&] { return msharp::usage(argv0); });
+}
+
+const char* msharp_parse_config(int argc, const char* const* argv) {
+  return guarded_text([&] { return msharp::config_to_json(msharp::parse_config(argc, argv)); });
+}
+
+const char* msharp_rack_from_yaml(const char* yaml_text) {
+  return guarded_text([&] { return msharp::rack_to_json(msharp::RackConfig::parse(yaml_text)); });
+}
+
+const char* msharp_rack_from_file(const char* path) {
+  return guarded_text([&] { return msharp::rack_to_json(msharp::RackConfig::load(path)); });
+}
+
+const char* msharp_plan_from_yaml(const char* yaml_text, int rank_count, const char* selection) {
+  return guarded_text([&] {
+    return msharp::plan_to_json(msharp::build_rank_plan(msharp::RackConfig::parse(yaml_text), rank_count, selection));
+  });
+}
+
+const char* msharp_launch_texts(const char* yaml_text, int rank_count, const char* selection, const char* ssh_user,
+                                const char* ssh_identity, const char* ssh_known_hosts) {
+  return guarded_text([&] {
+    const msharp::RackConfig rack = msharp::RackConfig::parse(yaml_text);
+    const msharp::RankPlan plan = msharp::build_rank_plan(rack, rank_count, selection);
+    msharp::SshOptions opt;
+    if (ssh_user != nullptr && *ssh_user) {
+      opt.user = ssh_user;
+    }
+    if (ssh_identity != nullptr && *ssh_identity) {
+      opt.identity = ssh_identity;
+    }
+    if (ssh_known_hosts != nullptr && *ssh_known_hosts) {
+      opt.known_hosts = ssh_known_hosts;
+    }
+    msharp::JsonWriter w;
+    w.begin_object();
+    w.key("hosts").value(msharp::host_list_text(plan));
+    w.key("rankfile").value(msharp::rankfile_text(plan));
+    w.key("ssh_config").value(msharp::ssh_config_text(rack, plan, opt));
+    w.key("entries").value(msharp::selected_entries_text(rack, plan));
+    w.key("rank_count").value(plan.size());
+    w.end_object();
+    return w.str();
+  });
+}
+
+const char* msharp_parse_cpu_list(const char* text) {
+  return guarded_text([&] {
+    msharp::JsonWriter w;
+    w.begin_array();
+    for (int c : msharp::parse_cpu_list(text)) {
+      w.value(c);
+    }
+    w.end_array();
+    return w.str();
+  });
+}
+
+const char* msharp_yaml_to_json(const char* yaml_text) {
+  return guarded_text([&] {
+    msharp::JsonWriter w;
+    yaml_to_json(msharp::parse_yaml(yaml_text), w);
+    return w.str();
+  });
+}
+
+const char* msharp_init_latency_csv_header(void) { return msharp::kInitLatencyCsvHeader; }
+
+const char* msharp_run_cpu_only(int argc, const char* const* argv) {
+  return guarded_text([&] {
+    msharp::Config cfg = msharp::parse_config(argc, argv);
+    std::ostringstream os;
+    msharp::run_cpu_only(cfg, os);
+    return os.str();
+  });
+}
+
+// ---------------------------------------------------------------------------- control plane
+void* msharp_bootstrap_connect(int rank, int world, const char* session, int timeout_ms) {
+  try {
+    msharp::BootstrapOptions opt;
+    opt.rank = rank;
+    opt.world = world;
+    opt.session = session != nullptr ? session : "default";
+    opt.timeout_ms = timeout_ms;
+    g_error.clear();
+    return msharp::Bootstrap::connect(opt).release();
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return nullptr;
+  }
+}
+
+void msharp_bootstrap_destroy(void* b) { delete static_cast<msharp::Bootstrap*>(b); }
+
+int msharp_bootstrap_barrier(void* b) {
+  return guarded([&] { static_cast<msharp::Bootstrap*>(b)->barrier(); });
+}
+
+int msharp_bootstrap_allgather(void* b, const void* send, void* recv, size_t bytes) {
+  return guarded([&] { static_cast<msharp::Bootstrap*>(b)->allgather(send, recv, bytes); });
+}
+
+int msharp_bootstrap_broadcast(void* b, void* buffer, size_t bytes, int root) {
+  return guarded([&] { static_cast<msharp::Bootstrap*>(b)->broadcast(buffer, bytes, root); });
+}
+
+int msharp_bootstrap_allgather_fd(void* b, int fd, int* out_fds) {
+  return guarded([&] {
+    const std::vector<int> fds = static_cast<msharp::Bootstrap*>(b)->allgather_fd(fd);
+    std::memcpy(out_fds, fds.data(), fds.size() * sizeof(int));
+  });
+}
+
+int msharp_bootstrap_abort(void* b, const char* reason) {
+  static_cast<msharp::Bootstrap*>(b)->abort(reason != nullptr ? reason : "");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------- fake driver
+void msharp_fake_driver_reset(int device_count) { msharp::fake_driver_reset(device_count); }
+
+void msharp_fake_driver_set_attribute(int attribute, int value) {
+  msharp::fake_driver_set_attribute(static_cast<CUdevice_attribute>(attribute), value);
+}
+
+void msharp_fake_driver_fail_call(const char* name, int nth, int cu_result) {
+  msharp::fake_driver_fail_call(name, nth, static_cast<CUresult>(cu_result));
+}
+
+const char* msharp_fake_driver_log(void) {
+  return guarded_text([&] {
+    msharp::JsonWriter w;
+    w.begin_array();
+    for (const auto& line : msharp::fake_driver_call_log()) {
+      w.value(line);
+    }
+    w.end_array();
+    return w.str();
+  });
+}
+
+int msharp_fake_driver_leaks(int* out) {
+  const msharp::FakeDriverLeaks l = msharp::fake_driver_leaks();
+  out[0] = l.handles;
+  out[1] = l.reservations;
+  out[2] = l.mappings;
+  out[3] = l.multicast_bindings;
+  return 0;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------- communicator
+extern "C" {
+
+void* msharp_comm_create(void* bootstrap, int device_ordinal, int wait_timeout_ms, int driver, int handle_type) {
+  try {
+    auto handle = std::make_unique<CommHandle>();
+    handle->bootstrap = static_cast<msharp::Bootstrap*>(bootstrap);
+    handle->api = driver == 1 ? &msharp::fake_driver() : &msharp::real_driver();
+    if (handle_type < 0 || handle_type > 2) {
+      throw std::invalid_argument("handle_type must be 0 (auto), 1 (posix_fd) or 2 (fabric)");
+    }
+    if (!handle->api->is_fake) {
+      MSHARP_CUDA(cudaSetDevice(device_ordinal));
+      MSHARP_CUDA(cudaFree(nullptr));
+    }
+    handle->rank.world_rank = handle->bootstrap->rank();
+    handle->rank.world_size = handle->bootstrap->world();
+    handle->rank.gpu_ordinal = device_ordinal;
+    handle->caps = msharp::query_capabilities(*handle->api, &handle->rank);
+    msharp::SymmOptions& base = handle->base;
+    base.handle_type = static_cast<msharp::HandleChoice>(handle_type);
+    base.device_ordinal = device_ordinal;
+    base.cu_device = handle->rank.cu_device;
+    base.posix_fd_supported = handle->caps.posix_fd_handle_supported;
+    base.fabric_supported = handle->caps.fabric_handle_supported;
+    base.multicast_supported = handle->caps.multicast_supported;
+    if (!handle->bootstrap->all_true(handle->caps.vmm_supported)) {
+      throw std::runtime_error("one or more GPUs lack virtual memory management support");
+    }
+    handle->ctx = msharp::CommContext::create(*handle->api, *handle->bootstrap, base, wait_timeout_ms);
+    g_error.clear();
+    return handle.release();
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return nullptr;
+  }
+}
+
+int msharp_comm_destroy(void* comm) {
+  return guarded([&] {
+    std::unique_ptr<CommHandle> handle(static_cast<CommHandle*>(comm));
+    if (handle && handle->ctx) {
+      if (!handle->api->is_fake) {
+        cudaDeviceSynchronize();
+      }
+      handle->ctx->destroy(handle->bootstrap);
+    }
+  });
+}
+
+const char* msharp_comm_info(void* comm) {
+  return guarded_text([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    msharp::JsonWriter w;
+    w.begin_object();
+    w.key("rank").value(h->rank.world_rank);
+    w.key("world").value(h->rank.world_size);
+    w.key("device").value(h->rank.gpu_ordinal);
+    w.key("host_numa_id").value(h->rank.host_numa_id);
+    w.key("driver_version").value(h->caps.driver_version);
+    w.key("vmm").value(h->caps.vmm_supported);
+    w.key("posix_fd").value(h->caps.posix_fd_handle_supported);
+    w.key("fabric").value(h->caps.fabric_handle_supported);
+    w.key("multicast").value(h->caps.multicast_supported);
+    w.key("bulk_multimem").value(h->caps.bulk_multimem_supported);
+    w.key("control_multicast").value(h->ctx->has_multicast());
+    w.key("multimem_barrier").value(h->ctx->device().use_multimem_barrier != 0);
+    w.key("nvfp4").value("unsupported");
+    w.key("mxfp4").value("unsupported");
+    w.end_object();
+    return w.str();
+  });
+}
+
+int msharp_comm_status(void* comm, uint32_t* out) {
+  return guarded([&] {
+    const msharp::DeviceStatus s = static_cast<CommHandle*>(comm)->ctx->read_status();
+    out[0] = s.bits;
+    out[1] = s.block;
+    out[2] = s.detail;
+  });
+}
+
+int msharp_comm_clear_status(void* comm) {
+  return guarded([&] { static_cast<CommHandle*>(comm)->ctx->clear_status(); });
+}
+
+int msharp_comm_reset(void* comm) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    h->ctx->reset(*h->bootstrap);
+  });
+}
+
+int msharp_comm_set_timeout_ms(void* comm, int ms) {
+  return guarded([&] { static_cast<CommHandle*>(comm)->ctx->set_timeout_ms(ms); });
+}
+
+int msharp_comm_set_multimem_barrier(void* comm, int enabled) {
+  return guarded([&] { static_cast<CommHandle*>(comm)->ctx->set_multimem_barrier(enabled != 0); });
+}
+
+// ---------------------------------------------------------------------------- symmetric memory
+void* msharp_symm_alloc(void* comm, size_t payload_bytes, int layout, int want_multicast) {
+  try {
+    auto* h = static_cast<CommHandle*>(comm);
+    auto symm = std::make_unique<SymmHandle>();
+    symm->comm = h;
+    msharp::SymmOptions opt = h->base;
+    opt.payload_bytes = payload_bytes;
+    opt.layout = layout == 1 ? msharp::RegionLayout::kInputOutput : msharp::RegionLayout::kSingle;
+    opt.want_multicast = want_multicast != 0;
+    symm->mem = msharp::SymmetricMemory::create(*h->api, *h->bootstrap, opt);
+    g_error.clear();
+    return symm.release();
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return nullptr;
+  }
+}
+
+int msharp_symm_free(void* symm) {
+  return guarded([&] {
+    std::unique_ptr<SymmHandle> h(static_cast<SymmHandle*>(symm));
+    if (h && h->mem) {
+      if (!h->comm->api->is_fake) {
+        cudaDeviceSynchronize();
+      }
+      h->comm->bootstrap->barrier();  // no peer kernel still touches this memory
+      h->mem->destroy();
+    }
+  });
+}
+
+const char* msharp_symm_info(void* symm) {
+  return guarded_text([&] {
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    msharp::JsonWriter w;
+    w.begin_object();
+    w.key("payload_bytes").value(static_cast<uint64_t>(m.payload_bytes));
+    w.key("allocation_bytes").value(static_cast<uint64_t>(m.alloc_bytes));
+    w.key("input_offset").value(static_cast<uint64_t>(m.input_offset));
+    w.key("output_offset").value(static_cast<uint64_t>(m.output_offset));
+    w.key("multicast_bytes").value(static_cast<uint64_t>(m.multicast_bytes));
+    w.key("vmm_granularity").value(static_cast<uint64_t>(m.vmm_granularity));
+    w.key("multicast_granularity").value(static_cast<uint64_t>(m.multicast_granularity));
+    w.key("multicast_bound").value(m.multicast_bound);
+    w.key("handle_type").value(m.handle_kind);
+    w.key("peer_init_local_ms").value(m.peer_init_local_ms);
+    w.key("peer_init_local_ms_by_rank").begin_array();
+    for (double v : m.peer_init_all_ms) {
+      w.value(v);
+    }
+    w.end_array();
+    const msharp::TimingStats s = msharp::summarize(m.peer_init_all_ms);
+    w.key("peer_init_ms").value(s.max);
+    w.key("peer_init_min_ms").value(s.min);
+    w.key("peer_init_median_ms").value(s.median);
+    w.key("peer_init_p95_ms").value(s.p95);
+    w.key("peer_init_max_ms").value(s.max);
+    w.end_object();
+    return w.str();
+  });
+}
+
+uint64_t msharp_symm_input_ptr(void* symm, int rank) {
+  const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+  return rank >= 0 && rank < m.world() ? static_cast<uint64_t>(m.input_ptr(rank)) : 0;
+}
+
+uint64_t msharp_symm_output_ptr(void* symm, int rank) {
+  const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+  return rank >= 0 && rank < m.world() ? static_cast<uint64_t>(m.output_ptr(rank)) : 0;
+}
+
+uint64_t msharp_symm_mc_ptr(void* symm) {
+  return static_cast<uint64_t>(static_cast<SymmHandle*>(symm)->mem->mc_output_ptr());
+}
+
+int msharp_symm_copy_to_host(void* symm, void* dst, int slot_rank, size_t offset, size_t bytes) {
+  return guarded([&] { static_cast<SymmHandle*>(symm)->mem->copy_to_host(dst, slot_rank, offset, bytes); });
+}
+
+int msharp_symm_copy_from_host(void* symm, int slot_rank, size_t offset, const void* src, size_t bytes) {
+  return guarded([&] { static_cast<SymmHandle*>(symm)->mem->copy_from_host(slot_rank, offset, src, bytes); });
+}
+
+// ---------------------------------------------------------------------------- kernels
+int msharp_init_pattern(int dtype, int pattern, uint64_t seed, int rank, uint64_t dst, size_t bytes, uint64_t stream) {
+  return guarded([&] {
+    msharp::launch_init_pattern(to_dtype(dtype), pattern, seed, rank, reinterpret_cast<void*>(dst), bytes, as_stream(stream));
+  });
+}
+
+int msharp_poison_fill(uint64_t dst, size_t bytes, uint64_t stream) {
+  return guarded([&] { msharp::launch_poison_fill(reinterpret_cast<void*>(dst), bytes, as_stream(stream)); });
+}
+
+int msharp_hash_device(uint64_t data, size_t bytes, uint64_t out_hash_device, uint64_t stream) {
+  return guarded([&] {
+    msharp::launch_hash(reinterpret_cast<const void*>(data), bytes, reinterpret_cast<uint64_t*>(out_hash_device),
+                        as_stream(stream));
+  });
+}
+
+int msharp_canary_check(void* comm, void* symm, uint64_t stream) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    const bool fake = h->api->is_fake;
+    const int world = m.world();
+    if (fake) {
+      auto* words = reinterpret_cast<uint32_t*>(static_cast<uintptr_t>(m.input_ptr(m.rank())));
+      for (int i = 0; i < msharp::kCanaryWords; ++i) {
+        words[i] = 0xC0010000u | ((static_cast<uint32_t>(m.rank()) & 0xffu) << 8) | static_cast<uint32_t>(i);
+      }
+    } else {
+      msharp::launch_canary_write(reinterpret_cast<uint32_t*>(m.input_ptr(m.rank())), m.rank(), as_stream(stream));
+      msharp::launch_alias_fence(as_stream(stream));
+      MSHARP_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    }
+    h->bootstrap->barrier();
+    std::string error;
+    for (int slot = 0; slot < world && error.empty(); ++slot) {
+      uint32_t words[msharp::kCanaryWords] = {0};
+      m.copy_to_host(words, slot, m.input_offset, sizeof(words));
+      for (int i = 0; i < msharp::kCanaryWords; ++i) {
+        const uint32_t expected = 0xC0010000u | ((static_cast<uint32_t>(slot) & 0xffu) << 8) | static_cast<uint32_t>(i);
+        if (words[i] != expected) {
+          std::ostringstream os;
+          os << "canary mismatch: rank " << m.rank() << " read slot " << slot << " word " << i << " = 0x" << std::hex
+             << words[i] << ", expected 0x" << expected;
+          error = os.str();
+          break;
+        }
+      }
+    }
+    if (!fake && error.empty()) {
+      msharp::PeerPointers slots{};
+      for (int r = 0; r < world; ++r) {
+        slots.ptr[r] = static_cast<uint64_t>(m.input_ptr(r));
+      }
+      msharp::launch_canary_verify(h->ctx->device(), slots, as_stream(stream));
+      MSHARP_CUDA(cudaStreamSynchronize(as_stream(stream)));
+      const msharp::DeviceStatus st = h->ctx->read_status();
+      if (st.bits != 0) {
+        error = msharp::describe_status(st);
+      }
+    }
+    const bool all_ok = h->bootstrap->all_true(error.empty());
+    if (!error.empty()) {
+      throw std::runtime_error(error);
+    }
+    if (!all_ok) {
+      throw std::runtime_error("canary check failed on another rank");
+    }
+  });
+}
+
+int msharp_allreduce_pull(void* comm, void* symm, int dtype, int acc_f32, size_t offset, size_t bytes, int grid,
+                          int block, int unroll, uint64_t stream) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    check_range(m, offset, bytes);
+    void* target;
+    if (m.world() == 1) {
+      target = reinterpret_cast<void*>(m.output_ptr(0) + offset);
+    } else {
+      if (m.mc_base == 0) {
+        throw std::runtime_error("pull all-reduce needs a buffer with a multicast alias");
+      }
+      target = reinterpret_cast<void*>(m.mc_output_ptr() + offset);
+    }
+    msharp::LaunchShape shape{grid, block, unroll};
+    msharp::launch_allreduce_pull(h->ctx->device(), to_dtype(dtype), acc_f32 ? msharp::PullAcc::kF32 : msharp::PullAcc::kNative,
+                                  target, bytes, shape, as_stream(stream));
+  });
+}
+
+int msharp_allreduce_sw_f32(void* comm, void* symm, size_t offset, size_t bytes, uint64_t in_scales_device,
+                            float out_scale_inv, int grid, int block, uint64_t stream) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    check_range(m, offset, bytes);
+    void* mc = m.mc_base != 0 ? reinterpret_cast<void*>(m.mc_output_ptr() + offset) : nullptr;
+    msharp::LaunchShape shape{grid, block, 0};
+    msharp::launch_allreduce_sw_f32(h->ctx->device(), outputs_of(m, offset), mc, bytes,
+                                    reinterpret_cast<const float*>(in_scales_device), out_scale_inv, shape,
+                                    as_stream(stream));
+  });
+}
+
+int msharp_allreduce_bulk_push(void* comm, void* symm, int dtype, size_t offset, size_t bytes, int grid,
+                               uint64_t stream) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    check_range(m, offset, bytes);
+    if (m.input_offset == m.output_offset) {
+      throw std::runtime_error("bulk push is out of place: allocate the buffer with the input/output layout");
+    }
+    msharp::LaunchShape shape{grid, 0, 0};
+    msharp::launch_allreduce_bulk_push(h->ctx->device(), to_dtype(dtype),
+                                       reinterpret_cast<const void*>(m.input_ptr(m.rank()) + offset), outputs_of(m, offset),
+                                       bytes, shape, as_stream(stream));
+  });
+}
+
+int msharp_allreduce_reference_geometry(void* symm, int dtype, size_t bytes, uint64_t stream) {
+  return guarded([&] {
+    const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
+    if (m.mc_base == 0) {
+      throw std::runtime_error("reference-geometry all-reduce needs a multicast alias");
+    }
+    check_range(m, 0, bytes);
+    msharp::launch_allreduce_reference_geometry(to_dtype(dtype), reinterpret_cast<void*>(m.mc_output_ptr()), bytes,
+                                                as_stream(stream));
+  });
+}
+
+int msharp_bulk_multimem_compiled(void) { return msharp::bulk_multimem_compiled() ? 1 : 0; }
+
+}  // extern "C"

@@ -1,0 +1,406 @@
+// One rank of the all-reduce benchmark.
+//
+// Step order follows the reference project's Run() (src/main.cc:389-486): plan, topology,
+// capabilities, NUMA pin, mapping validation, symmetric memory with its timed peer-init phase,
+// canary smoke test, optional early exit for --init-only, warm-up and measured iterations,
+// replica hashes, CPU check of the first --reference-check-bytes on rank 0, report, status
+// broadcast, teardown. What differs:
+//   * the collective kernels carry their own cross-GPU barriers, so the CUDA-event time of
+//     every rank covers the whole collective and the reported time is the maximum over ranks
+//     (the reference times rank 0's kernel only for its legacy backend, src/main.cc:97-111);
+//   * the output buffer is poison-filled before every iteration of an out-of-place backend so
+//     that untouched bytes cannot pass the check;
+//   * device-side wait failures are read back after every iteration and raised on all ranks.
+#include "msharp/runner.h"
+
+#include <cuda_runtime_api.h>
+
+#include <chrono>
+#include <cstdlib>
+#include <iostream>
+#include <memory>
+#include <sstream>
+#include <stdexcept>
+
+#include "msharp/comm_context.h"
+#include "msharp/json.h"
+#include "msharp/kernels.h"
+#include "msharp/numerics.h"
+#include "msharp/rack.h"
+#include "msharp/report.h"
+#include "msharp/symm_mem.h"
+#include "msharp/topology.h"
+
+namespace msharp {
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+double ms_since(Clock::time_point t0) { return std::chrono::duration<double, std::milli>(Clock::now() - t0).count(); }
+
+struct RankRun {
+  const Config& cfg;
+  Bootstrap& comm;
+  const DriverApi& api;
+  RankInfo rank;
+  CapabilityInfo caps;
+  std::unique_ptr<CommContext> ctx;
+  std::unique_ptr<SymmetricMemory> mem;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t start = nullptr;
+  cudaEvent_t stop = nullptr;
+  Dtype dtype = Dtype::kE4M3;
+  int pattern = 0;
+  LaunchShape shape;
+  std::string kernel_variant;
+  std::string bulk_variant;
+
+  void* input_ptr() const { return reinterpret_cast<void*>(mem->input_ptr(rank.world_rank)); }
+  void* output_ptr() const { return reinterpret_cast<void*>(mem->output_ptr(rank.world_rank)); }
+  PeerPointers outputs() const {
+    PeerPointers p{};
+    for (int r = 0; r < rank.world_size; ++r) {
+      p.ptr[r] = static_cast<uint64_t>(mem->output_ptr(r));
+    }
+    return p;
+  }
+};
+
+// Raise on every rank if any rank's kernel left a status bit behind.
+void agree_on_device_status(RankRun& run, const char* what) {
+  const DeviceStatus st = run.ctx->read_status();
+  const bool all_ok = run.comm.all_true(st.bits == 0);
+  if (st.bits != 0) {
+    throw std::runtime_error(std::string(what) + ": " + describe_status(st));
+  }
+  if (!all_ok) {
+    throw std::runtime_error(std::string(what) + ": a device-side wait failed on another rank");
+  }
+}
+
+void canary_smoke_test(RankRun& run) {
+  const int world = run.rank.world_size;
+  launch_canary_write(static_cast<uint32_t*>(run.input_ptr()), run.rank.world_rank, run.stream);
+  launch_alias_fence(run.stream);
+  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  run.comm.barrier();
+  // host view: copy the canary of every slot (own and peers) through the unicast mappings
+  for (int slot = 0; slot < world; ++slot) {
+    uint32_t words[kCanaryWords] = {0};
+    run.mem->copy_to_host(words, slot, run.mem->input_offset, sizeof(words));
+    for (int i = 0; i < kCanaryWords; ++i) {
+      const uint32_t expected = 0xC0010000u | ((static_cast<uint32_t>(slot) & 0xffu) << 8) | static_cast<uint32_t>(i);
+      if (words[i] != expected) {
+        std::ostringstream os;
+        os << "canary mismatch: rank " << run.rank.world_rank << " read slot " << slot << " word " << i << " = 0x"
+           << std::hex << words[i] << ", expected 0x" << expected;
+        throw std::runtime_error(os.str());
+      }
+    }
+  }
+  // device view: a kernel reads every slot after a device barrier
+  PeerPointers slots{};
+  for (int r = 0; r < world; ++r) {
+    slots.ptr[r] = static_cast<uint64_t>(run.mem->input_ptr(r));
+  }
+  launch_canary_verify(run.ctx->device(), slots, run.stream);
+  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  agree_on_device_status(run, "canary smoke test");
+  run.comm.barrier();
+}
+
+void initialize_buffers(RankRun& run) {
+  const Config& cfg = run.cfg;
+  launch_init_pattern(run.dtype, run.pattern, cfg.seed, run.rank.world_rank, run.input_ptr(), cfg.bytes, run.stream);
+  if (cfg.sharp_backend == Backend::kTmaAsync) {
+    launch_poison_fill(run.output_ptr(), cfg.bytes, run.stream);
+    launch_async_proxy_fence(run.stream);
+  }
+  launch_alias_fence(run.stream);
+  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+}
+
+void launch_collective(RankRun& run) {
+  const Config& cfg = run.cfg;
+  const DeviceComm dc = run.ctx->device();
+  const int world = run.rank.world_size;
+  switch (cfg.sharp_backend) {
+    case Backend::kLegacy:
+    case Backend::kPull: {
+      void* target = world == 1 ? run.output_ptr() : reinterpret_cast<void*>(run.mem->mc_output_ptr());
+      if (cfg.reference_geometry && world > 1) {
+        if (run.rank.world_rank == 0) {
+          launch_allreduce_reference_geometry(run.dtype, target, cfg.bytes, run.stream);
+        }
+      } else {
+        const PullAcc acc = resolve_acc(cfg) == AccChoice::kF32 ? PullAcc::kF32 : PullAcc::kNative;
+        launch_allreduce_pull(dc, run.dtype, acc, target, cfg.bytes, run.shape, run.stream);
+      }
+      break;
+    }
+    case Backend::kSwF32: {
+      void* mc = world == 1 || run.mem->mc_base == 0 ? nullptr : reinterpret_cast<void*>(run.mem->mc_output_ptr());
+      launch_allreduce_sw_f32(dc, run.outputs(), mc, cfg.bytes, nullptr, 1.0f, run.shape, run.stream);
+      break;
+    }
+    case Backend::kTmaAsync:
+      launch_allreduce_bulk_push(dc, run.dtype, run.input_ptr(), run.outputs(), cfg.bytes, run.shape, run.stream);
+      break;
+  }
+}
+
+void run_iteration(RankRun& run, bool measure, double* device_ms, double* wall_ms) {
+  initialize_buffers(run);
+  run.comm.barrier();  // every rank's input is in place
+  const auto t0 = Clock::now();
+  if (measure) {
+    MSHARP_CUDA(cudaEventRecord(run.start, run.stream));
+  }
+  launch_collective(run);
+  if (measure) {
+    MSHARP_CUDA(cudaEventRecord(run.stop, run.stream));
+  }
+  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  run.comm.barrier();
+  const double local_wall = ms_since(t0);
+  agree_on_device_status(run, "all-reduce kernel");
+  if (measure) {
+    float local_ms = 0.0f;
+    MSHARP_CUDA(cudaEventElapsedTime(&local_ms, run.start, run.stop));
+    *device_ms = run.comm.reduce_max(static_cast<double>(local_ms));
+    *wall_ms = run.comm.reduce_max(local_wall);
+  }
+}
+
+int tolerance_for(const Config& cfg, int world) {
+  if (cfg.sharp_backend == Backend::kSwF32) {
+    return 0;  // float32 sum in rank order, one final rounding: identical to the host model
+  }
+  if (cfg.sharp_backend == Backend::kTmaAsync) {
+    return world;  // memory-side adds in the element type, arrival order not fixed
+  }
+  if (resolve_type(cfg) == TypeChoice::kE4M3) {
+    return 1;  // fp16 accumulation in the switch, then one FP8 rounding
+  }
+  return resolve_acc(cfg) == AccChoice::kF32 ? 1 : world;
+}
+
+}  // namespace
+
+int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostream& out) {
+  const RackConfig rack = RackConfig::load(cfg.rack_config_path);
+  const int world = comm.world();
+  const int selected = cfg.rank_count.value_or(world);
+  const RankPlan plan = build_rank_plan(rack, selected, cfg.rank_selection);
+
+  const char* label_env = std::getenv("MNNVL_HOST_LABEL");
+  RankRun run{cfg, comm, api, {}, {}, nullptr, nullptr, nullptr, nullptr, nullptr, Dtype::kE4M3, 0, {}, {}, {}};
+  run.rank = discover_rank_info(comm.rank(), world, rack, plan, label_env != nullptr ? label_env : "");
+  MSHARP_CUDA(cudaSetDevice(run.rank.gpu_ordinal));
+  MSHARP_CUDA(cudaFree(nullptr));  // creates the primary context that the driver calls below use
+  run.caps = query_capabilities(api, &run.rank);
+  if (!cfg.no_pin) {
+    pin_thread_to_numa(run.rank.host_numa_id);
+  }
+  const std::vector<RankMappingRecord> records = gather_rank_mappings(comm, run.rank);
+  validate_rank_mappings(records, rack, plan);
+  validate_capabilities(comm, run.caps, cfg.sharp_backend, world);
+
+  run.dtype = resolve_dtype(cfg);
+  run.pattern = pattern_id(cfg.pattern);
+  run.shape.grid = cfg.grid;
+  run.shape.block = cfg.block;
+  run.shape.unroll = cfg.unroll;
+
+  MSHARP_CUDA(cudaStreamCreateWithFlags(&run.stream, cudaStreamNonBlocking));
+  MSHARP_CUDA(cudaEventCreate(&run.start));
+  MSHARP_CUDA(cudaEventCreate(&run.stop));
+
+  SymmOptions base;
+  base.handle_type = cfg.handle_type;
+  base.device_ordinal = run.rank.gpu_ordinal;
+  base.cu_device = run.rank.cu_device;
+  base.posix_fd_supported = run.caps.posix_fd_handle_supported;
+  base.fabric_supported = run.caps.fabric_handle_supported;
+  base.multicast_supported = run.caps.multicast_supported;
+
+  RunReport report;
+  report.cfg = cfg;
+  report.caps = run.caps;
+  report.records = records;
+
+  int status = 0;
+  std::string failure;
+  try {
+    const auto c0 = Clock::now();
+    run.ctx = CommContext::create(api, comm, base, cfg.wait_timeout_ms);
+    report.control_init_ms = ms_since(c0);
+
+    SymmOptions data = base;
+    data.payload_bytes = cfg.bytes;
+    data.layout = cfg.sharp_backend == Backend::kTmaAsync ? RegionLayout::kInputOutput : RegionLayout::kSingle;
+    // the fan-out form of the bulk backend and the software path write through unicast mappings
+    data.want_multicast = cfg.sharp_backend != Backend::kTmaAsync || bulk_multimem_compiled();
+    run.mem = SymmetricMemory::create(api, comm, data);
+    if ((cfg.sharp_backend == Backend::kLegacy || cfg.sharp_backend == Backend::kPull) && world > 1 &&
+        run.mem->mc_base == 0) {
+      throw std::runtime_error("the multicast alias could not be created; this backend needs it");
+    }
+
+    report.allocation_bytes = run.mem->alloc_bytes;
+    report.input_offset = run.mem->input_offset;
+    report.output_offset = run.mem->output_offset;
+    report.multicast_bytes = run.mem->multicast_bytes;
+    report.vmm_granularity = run.mem->vmm_granularity;
+    report.multicast_granularity = run.mem->multicast_granularity;
+    report.peer_init = summarize(run.mem->peer_init_all_ms);
+    report.peer_init_by_rank = run.mem->peer_init_all_ms;
+    report.handle_kind = run.mem->handle_kind;
+    switch (cfg.sharp_backend) {
+      case Backend::kLegacy:
+      case Backend::kPull:
+        report.kernel_variant = world == 1 ? "local_copy"
+                                : cfg.reference_geometry ? "reference_geometry_rank0_b32"
+                                                         : "multimem_ld_reduce_st_v4_sliced";
+        break;
+      case Backend::kSwF32:
+        report.kernel_variant = run.mem->mc_base != 0 ? "peer_loads_f32_multimem_st" : "peer_loads_f32_peer_stores";
+        break;
+      case Backend::kTmaAsync:
+        report.kernel_variant = "bulk_ring_store_reduce";
+        report.bulk_variant = "unicast_fanout";
+        break;
+    }
+
+    canary_smoke_test(run);
+
+    if (!cfg.init_only) {
+      for (int i = 0; i < cfg.warmup; ++i) {
+        run_iteration(run, false, nullptr, nullptr);
+      }
+      std::vector<double> device_times;
+      std::vector<double> wall_times;
+      for (int i = 0; i < cfg.iters; ++i) {
+        double d = 0.0;
+        double w = 0.0;
+        run_iteration(run, true, &d, &w);
+        device_times.push_back(d);
+        wall_times.push_back(w);
+      }
+      if (cfg.iters == 0) {
+        run_iteration(run, false, nullptr, nullptr);  // the check below needs one result
+      }
+
+      uint64_t* device_hash = run.ctx->scratch_u64();
+      launch_hash(run.output_ptr(), cfg.bytes, device_hash, run.stream);
+      uint64_t local_hash = 0;
+      MSHARP_CUDA(cudaMemcpyAsync(&local_hash, device_hash, sizeof(local_hash), cudaMemcpyDeviceToHost, run.stream));
+      MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+      report.hashes = comm.allgather_u64(local_hash);
+      report.has_results = true;
+      report.device_ms = summarize(device_times);
+      report.wall_ms = summarize(wall_times);
+
+      if (comm.rank() == 0) {
+        std::vector<unsigned char> checked(cfg.reference_check_bytes);
+        run.mem->copy_to_host(checked.data(), 0, run.mem->output_offset, checked.size());
+        InputSpec spec;
+        spec.pattern = run.pattern;
+        spec.seed = cfg.seed;
+        spec.ranks = world;
+        const std::size_t elements = cfg.reference_check_bytes / dtype_size(run.dtype);
+        report.metrics = compare(run.dtype, spec, checked.data(), elements);
+        report.tolerance_ulp = tolerance_for(cfg, world);
+        report.within_tolerance = report.metrics.max_requantized_ulp_distance <= report.tolerance_ulp;
+        if (report.metrics.exact_mismatches != 0 && std::getenv("MNNVL_DEBUG_MISMATCH") != nullptr) {
+          std::cerr << mismatch_dump(run.dtype, spec, checked.data(), elements) << "\n";
+        }
+      }
+    }
+
+    if (comm.rank() == 0) {
+      // grid/block as launched are reported by the launcher's own choice when left at 0
+      report.grid = cfg.grid;
+      report.block = cfg.block;
+      out << (cfg.json ? json_report(report) : human_report(report));
+      if (cfg.json) {
+        out << "\n";
+      }
+      out.flush();
+      status = final_status(report);
+    }
+    status = comm.broadcast_int(status, 0);
+  } catch (const std::exception& ex) {
+    failure = ex.what();
+  }
+
+  // Teardown in order on every path: no rank unmaps while a peer's kernel may still run.
+  cudaStreamSynchronize(run.stream);
+  if (failure.empty()) {
+    try {
+      comm.barrier();
+    } catch (const std::exception& ex) {
+      failure = ex.what();
+    }
+  }
+  if (run.mem) {
+    run.mem->destroy();
+  }
+  if (run.ctx) {
+    run.ctx->destroy(nullptr);
+  }
+  cudaEventDestroy(run.stop);
+  cudaEventDestroy(run.start);
+  cudaStreamDestroy(run.stream);
+  if (!failure.empty()) {
+    throw std::runtime_error(failure);
+  }
+  return status;
+}
+
+int run_cpu_only(const Config& cfg, std::ostream& out) {
+  const RackConfig rack = RackConfig::load(cfg.rack_config_path);
+  const int ranks = cfg.rank_count.value_or(static_cast<int>(rack.available_rank_count()));
+  const RankPlan plan = build_rank_plan(rack, ranks, cfg.rank_selection);
+  const Dtype dtype = resolve_dtype(cfg);
+  InputSpec spec;
+  spec.pattern = pattern_id(cfg.pattern);
+  spec.seed = cfg.seed;
+  spec.ranks = ranks;
+  const std::size_t elements = cfg.bytes / dtype_size(dtype);
+
+  std::vector<unsigned char> expected(cfg.bytes);
+  const auto t0 = Clock::now();
+  reduce_f32_cast(dtype, spec, 0, elements, expected.data());
+  const double f32_ms = ms_since(t0);
+  std::vector<unsigned char> semantic(cfg.bytes);
+  const auto t1 = Clock::now();
+  reduce_semantic(dtype, spec, 0, elements, semantic.data());
+  const double semantic_ms = ms_since(t1);
+  const PrecisionMetrics m = compare(dtype, spec, expected.data(), std::min(elements, cfg.reference_check_bytes / dtype_size(dtype)));
+  const uint64_t hash_f32 = hash_words(reinterpret_cast<const uint32_t*>(expected.data()), cfg.bytes / 4);
+  const uint64_t hash_sem = hash_words(reinterpret_cast<const uint32_t*>(semantic.data()), cfg.bytes / 4);
+
+  JsonWriter w;
+  w.begin_object();
+  w.key("mode").value("cpu_only");
+  w.key("selected_rank_count").value(ranks);
+  w.key("rank_selection").value(cfg.rank_selection);
+  w.key("datatype").value(dtype_name(dtype));
+  w.key("pattern").value(cfg.pattern);
+  w.key("seed").value(cfg.seed);
+  w.key("payload_bytes").value(static_cast<uint64_t>(cfg.bytes));
+  w.key("plan").raw(plan_to_json(plan));
+  w.key("expected_f32_cast_hash").value([&] { std::ostringstream os; os << std::hex << hash_f32; return os.str(); }());
+  w.key("expected_semantic_hash").value([&] { std::ostringstream os; os << std::hex << hash_sem; return os.str(); }());
+  w.key("f32_cast_vs_semantic_mismatches").value(static_cast<uint64_t>(m.exact_mismatches));
+  w.key("f32_requantized_mismatches").value(static_cast<uint64_t>(m.requantized_mismatches));
+  w.key("cpu_reduce_f32_ms").value(f32_ms);
+  w.key("cpu_reduce_semantic_ms").value(semantic_ms);
+  w.key("cpu_threads").value(default_threads());
+  w.end_object();
+  out << w.str() << "\n";
+  return 0;
+}
+
+}  // namespace msharp

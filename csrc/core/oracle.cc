@@ -209,7 +209,7 @@ PrecisionMetrics compare(Dtype dtype, const InputSpec& spec, const void* result,
     threads = default_threads();
   }
   struct Partial {
-    std::size_t exact = 0, requant = 0;
+    std::size_t exact = 0, requant = 0, switch_model = 0;
     int ulp = 0;
     float max_err = 0.0f;
     double sum_err = 0.0;
@@ -220,7 +220,24 @@ PrecisionMetrics compare(Dtype dtype, const InputSpec& spec, const void* result,
     Partial p;
     for (std::size_t i = b; i < e; ++i) {
       const uint32_t got = load_code(dtype, result, i);
-      const uint32_t want_semantic = encode_code(dtype, semantic_sum(dtype, spec, i));
+      const float sequential = semantic_sum(dtype, spec, i);
+      const uint32_t want_semantic = encode_code(dtype, sequential);
+      // In-switch FP8: the value just below or just above the sum is accepted; a sum that is
+      // representable must come back as itself; beyond +-448 the switch may answer NaN.
+      bool switch_ok = got == want_semantic;
+      if (!switch_ok && dtype == Dtype::kE4M3) {
+        const float nearest = decode_code(dtype, want_semantic);
+        if ((got & 0x7fu) == 0x7fu) {
+          switch_ok = std::fabs(sequential) > 448.0f;
+        } else if (nearest == sequential) {
+          switch_ok = decode_code(dtype, got) == sequential;  // covers -0 vs +0
+        } else {
+          const float other = decode_code(dtype, got);
+          const int step = std::abs(ordered_code(dtype, got) - ordered_code(dtype, want_semantic));
+          switch_ok = step == 1 && (other - sequential) * (nearest - sequential) < 0.0f;
+        }
+      }
+      p.switch_model += !switch_ok;
       const float sum32 = f32_sum(dtype, spec, i);
       const uint32_t want_requant = encode_code(dtype, sum32);
       p.exact += got != want_semantic;
@@ -241,6 +258,7 @@ PrecisionMetrics compare(Dtype dtype, const InputSpec& spec, const void* result,
   bool nan_err = false;
   for (const auto& p : partials) {
     m.exact_mismatches += p.exact;
+    m.switch_model_mismatches += p.switch_model;
     m.requantized_mismatches += p.requant;
     m.max_requantized_ulp_distance = std::max(m.max_requantized_ulp_distance, p.ulp);
     m.max_abs_error = std::max(m.max_abs_error, p.max_err);

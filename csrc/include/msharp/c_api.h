@@ -1,0 +1,99 @@
+// C interface of libmsharp.so, used by the Python package through ctypes and usable from any
+// language. Conventions: functions that can fail return 0 on success and a non-zero code on
+// failure, or a null pointer for pointer-returning functions; the message is then available
+// from msharp_last_error() (per thread). Returned strings live until the next call on the same
+// thread. The reference project has no library interface (it is a single binary).
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* msharp_last_error(void);
+const char* msharp_version(void);
+
+// ---- numerics and host oracle (dtype: 0 e4m3, 1 f16, 2 bf16; pattern: 0 reference, 1 seeded, 2 tagged)
+int msharp_encode(int dtype, const float* in, void* out, size_t n);
+int msharp_decode(int dtype, const void* in, float* out, size_t n);
+int msharp_generate(int dtype, int pattern, uint64_t seed, int rank, size_t first, size_t n, void* out);
+int msharp_reduce_f32(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, float* out);
+int msharp_reduce_f32_cast(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, void* out);
+int msharp_reduce_semantic(int dtype, int pattern, uint64_t seed, int ranks, size_t first, size_t n, void* out);
+int msharp_reduce_arrays_f32(int dtype, const void* const* inputs, int ranks, size_t n, float* out);
+// metrics[6] = exact_mismatches, requantized_mismatches, max_ulp_distance, max_abs_error, mean_abs_error,
+//              switch_model_mismatches
+int msharp_compare(int dtype, int pattern, uint64_t seed, int ranks, const void* result, size_t n, double* metrics);
+uint64_t msharp_hash_words(const uint32_t* words, size_t word_count);
+int msharp_summarize(const double* values, size_t n, double* min_median_p95_max);
+
+// ---- configuration, inventory, plan (JSON text out)
+const char* msharp_usage(const char* argv0);
+const char* msharp_parse_config(int argc, const char* const* argv);
+const char* msharp_rack_from_yaml(const char* yaml_text);
+const char* msharp_rack_from_file(const char* path);
+const char* msharp_plan_from_yaml(const char* yaml_text, int rank_count, const char* selection);
+// {"hosts": "...", "rankfile": "...", "ssh_config": "...", "entries": "..."}
+const char* msharp_launch_texts(const char* yaml_text, int rank_count, const char* selection, const char* ssh_user,
+                                const char* ssh_identity, const char* ssh_known_hosts);
+const char* msharp_parse_cpu_list(const char* text);
+const char* msharp_yaml_to_json(const char* yaml_text);
+const char* msharp_init_latency_csv_header(void);
+// Runs the host-only oracle program (same as the binary with --cpu-only); returns its JSON line.
+const char* msharp_run_cpu_only(int argc, const char* const* argv);
+
+// ---- control plane
+void* msharp_bootstrap_connect(int rank, int world, const char* session, int timeout_ms);
+void msharp_bootstrap_destroy(void* bootstrap);
+int msharp_bootstrap_barrier(void* bootstrap);
+int msharp_bootstrap_allgather(void* bootstrap, const void* send, void* recv, size_t bytes_per_rank);
+int msharp_bootstrap_broadcast(void* bootstrap, void* buffer, size_t bytes, int root);
+int msharp_bootstrap_allgather_fd(void* bootstrap, int fd, int* out_fds);
+int msharp_bootstrap_abort(void* bootstrap, const char* reason);
+
+// ---- fake driver (CPU tests)
+void msharp_fake_driver_reset(int device_count);
+void msharp_fake_driver_set_attribute(int attribute, int value);
+void msharp_fake_driver_fail_call(const char* name, int nth, int cu_result);
+const char* msharp_fake_driver_log(void);
+int msharp_fake_driver_leaks(int* handles_reservations_mappings_bindings);
+
+// ---- communicator and symmetric memory (driver: 0 real, 1 fake)
+void* msharp_comm_create(void* bootstrap, int device_ordinal, int wait_timeout_ms, int driver, int handle_type);
+int msharp_comm_destroy(void* comm);  // collective
+const char* msharp_comm_info(void* comm);
+int msharp_comm_status(void* comm, uint32_t* bits_block_detail);
+int msharp_comm_clear_status(void* comm);
+int msharp_comm_reset(void* comm);  // collective
+int msharp_comm_set_timeout_ms(void* comm, int ms);
+int msharp_comm_set_multimem_barrier(void* comm, int enabled);
+
+void* msharp_symm_alloc(void* comm, size_t payload_bytes, int layout, int want_multicast);
+int msharp_symm_free(void* symm);  // collective
+const char* msharp_symm_info(void* symm);
+uint64_t msharp_symm_input_ptr(void* symm, int rank);
+uint64_t msharp_symm_output_ptr(void* symm, int rank);
+uint64_t msharp_symm_mc_ptr(void* symm);
+int msharp_symm_copy_to_host(void* symm, void* dst, int slot_rank, size_t offset, size_t bytes);
+int msharp_symm_copy_from_host(void* symm, int slot_rank, size_t offset, const void* src, size_t bytes);
+
+// ---- kernels (stream: a cudaStream_t passed as an integer; 0 = default stream)
+int msharp_init_pattern(int dtype, int pattern, uint64_t seed, int rank, uint64_t dst, size_t bytes, uint64_t stream);
+int msharp_poison_fill(uint64_t dst, size_t bytes, uint64_t stream);
+int msharp_hash_device(uint64_t data, size_t bytes, uint64_t out_hash_device, uint64_t stream);
+int msharp_canary_check(void* comm, void* symm, uint64_t stream);  // write, verify on host and device; collective
+// in-place all-reduce over the output region of `symm`; offset/bytes select a sub-range
+int msharp_allreduce_pull(void* comm, void* symm, int dtype, int acc_f32, size_t offset, size_t bytes, int grid,
+                          int block, int unroll, uint64_t stream);
+int msharp_allreduce_sw_f32(void* comm, void* symm, size_t offset, size_t bytes, uint64_t in_scales_device,
+                            float out_scale_inv, int grid, int block, uint64_t stream);
+int msharp_allreduce_bulk_push(void* comm, void* symm, int dtype, size_t offset, size_t bytes, int grid,
+                               uint64_t stream);
+int msharp_allreduce_reference_geometry(void* symm, int dtype, size_t bytes, uint64_t stream);
+int msharp_bulk_multimem_compiled(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -54,6 +54,7 @@ class CommContext {
   CommContext() = default;
   std::unique_ptr<SymmetricMemory> block_;
   DeviceComm device_;
+  bool fake_ = false;
 };
 
 }  // namespace msharp

@@ -34,6 +34,11 @@ struct PrecisionMetrics {
   int max_requantized_ulp_distance = 0;    // in representable-value steps
   float max_abs_error = 0.0f;              // vs the float32 sum
   double mean_abs_error = 0.0;
+  // FP8 only: results that are neither the representable value just below nor the one just
+  // above the sequential-fp16 sum (a representable sum must come back unchanged). Measured on
+  // B200: multimem.ld_reduce .acc::f16.e4m3x4 returns either neighbour, not the nearest one,
+  // and NaN instead of +-448 on overflow. Equals exact_mismatches for the 16-bit types.
+  std::size_t switch_model_mismatches = 0;
 };
 
 struct TimingStats {

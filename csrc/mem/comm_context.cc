@@ -6,6 +6,40 @@
 #include <vector>
 
 namespace msharp {
+namespace {
+
+// With the host-memory fake driver the "device" pointers are ordinary host pointers.
+void fill_zero(bool fake, void* p, std::size_t bytes) {
+  if (fake) {
+    std::memset(p, 0, bytes);
+  } else {
+    MSHARP_CUDA(cudaMemset(p, 0, bytes));
+  }
+}
+
+void copy_in(bool fake, void* dst, const void* src, std::size_t bytes) {
+  if (fake) {
+    std::memcpy(dst, src, bytes);
+  } else {
+    MSHARP_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+  }
+}
+
+void copy_out(bool fake, void* dst, const void* src, std::size_t bytes) {
+  if (fake) {
+    std::memcpy(dst, src, bytes);
+  } else {
+    MSHARP_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+  }
+}
+
+void device_sync(bool fake) {
+  if (!fake) {
+    MSHARP_CUDA(cudaDeviceSynchronize());
+  }
+}
+
+}  // namespace
 
 std::string describe_status(const DeviceStatus& s) {
   if (s.bits == 0) {
@@ -47,14 +81,14 @@ std::unique_ptr<CommContext> CommContext::create(const DriverApi& api, Bootstrap
     throw std::runtime_error("control block is smaller than its layout");
   }
   auto* local = reinterpret_cast<unsigned char*>(b.uc_slots[static_cast<std::size_t>(b.rank())]);
-  MSHARP_CUDA(cudaMemset(local, 0, kCtrlBytes));
+  ctx->fake_ = api.is_fake;
+  fill_zero(ctx->fake_, local, kCtrlBytes);
   std::vector<uint64_t> table(kMaxWorld, 0);
   for (int r = 0; r < b.world(); ++r) {
     table[static_cast<std::size_t>(r)] = static_cast<uint64_t>(b.uc_slots[static_cast<std::size_t>(r)]);
   }
-  MSHARP_CUDA(cudaMemcpy(local + kCtrlPeerTableOffset, table.data(), table.size() * sizeof(uint64_t),
-                         cudaMemcpyHostToDevice));
-  MSHARP_CUDA(cudaDeviceSynchronize());
+  copy_in(ctx->fake_, local + kCtrlPeerTableOffset, table.data(), table.size() * sizeof(uint64_t));
+  device_sync(ctx->fake_);
   comm.barrier();  // nobody signals into a block that is still being zeroed
 
   ctx->device_.rank = b.rank();
@@ -95,11 +129,11 @@ void CommContext::set_timeout_ms(int ms) {
 
 DeviceStatus CommContext::read_status() const {
   uint32_t words[3] = {0, 0, 0};
-  MSHARP_CUDA(cudaMemcpy(words, device_.ctrl_local + kCtrlStatusOffset, sizeof(words), cudaMemcpyDeviceToHost));
+  copy_out(fake_, words, device_.ctrl_local + kCtrlStatusOffset, sizeof(words));
   return DeviceStatus{words[0], words[1], words[2]};
 }
 
-void CommContext::clear_status() { MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlStatusOffset, 0, 64)); }
+void CommContext::clear_status() { fill_zero(fake_, device_.ctrl_local + kCtrlStatusOffset, 64); }
 
 void CommContext::throw_if_failed(const char* what) const {
   const DeviceStatus s = read_status();
@@ -109,12 +143,12 @@ void CommContext::throw_if_failed(const char* what) const {
 }
 
 void CommContext::reset(Bootstrap& comm) {
-  MSHARP_CUDA(cudaDeviceSynchronize());
+  device_sync(fake_);
   comm.barrier();  // no kernel anywhere still signals
-  MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlCounterOffset, 0, kCtrlPeerTableOffset));
-  MSHARP_CUDA(cudaMemset(device_.ctrl_local + kCtrlEpochOffset, 0, kMaxBarrierSlots * sizeof(uint32_t)));
+  fill_zero(fake_, device_.ctrl_local + kCtrlCounterOffset, kCtrlPeerTableOffset);
+  fill_zero(fake_, device_.ctrl_local + kCtrlEpochOffset, kMaxBarrierSlots * sizeof(uint32_t));
   clear_status();
-  MSHARP_CUDA(cudaDeviceSynchronize());
+  device_sync(fake_);
   comm.barrier();
 }
 

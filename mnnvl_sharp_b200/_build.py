@@ -1,0 +1,166 @@
+"""In-tree build of the native parts: `libmsharp.so`, the `mnnvl_sharp_allreduce` binary,
+the C++ unit-test runner and (optionally) the PyTorch operator library.
+
+Everything is compiled for sm_100a only, with explicit `-gencode arch=compute_100a,code=sm_100a`
+(the `-arch=sm_100a` shorthand also emits plain compute_100 PTX, which cannot hold the FP8
+multimem forms). Objects are rebuilt when their source or any header is newer.
+
+The reference project's build (CMakeLists.txt:39-48 arch choice, :50-77 compile probe of the
+multimem bulk instruction, :95-98 feature defines) is mirrored by `probe_bulk_multimem()`.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+OUT = Path(__file__).resolve().parent / "_C"
+OBJ = ROOT / "build" / "obj"
+
+NVCC = os.environ.get("MNNVL_CUDA_COMPILER", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+CUDA_HOME = Path(NVCC).resolve().parent.parent
+GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", "-g1"]
+NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"] + GENCODE
+INCLUDES = ["-I", str(CSRC / "include"), "-I", str(CSRC / "kernels"), "-I", str(CUDA_HOME / "include")]
+
+LIB_SOURCES = [
+    "core/oracle.cc", "core/config.cc", "core/json.cc", "core/yaml_lite.cc", "core/rack.cc", "core/report.cc",
+    "comm/bootstrap.cc", "comm/spawn.cc",
+    "mem/driver_api.cc", "mem/fake_driver.cc", "mem/topology.cc", "mem/symm_mem.cc", "mem/comm_context.cc",
+    "kernels/util_kernels.cu", "kernels/allreduce_kernels.cu",
+    "app/runner.cc", "app/c_api.cc",
+]
+OPTIONAL_LIB_SOURCES = ["kernels/gemm_allreduce.cu", "kernels/no_alloc.cu"]
+
+
+def _run(cmd: list[str]) -> None:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+
+
+def probe_bulk_multimem() -> bool:
+    """Does this nvcc assemble `multimem.cp.reduce.async.bulk`? (needs PTX ISA 9.1)"""
+    src = (
+        "#include <cstdint>\n"
+        "__global__ void k(void* dst, uint32_t bytes) {\n"
+        "  extern __shared__ __align__(128) unsigned char tile[];\n"
+        "  asm volatile(\"multimem.cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;\"\n"
+        "               :: \"l\"(dst), \"r\"((uint32_t)__cvta_generic_to_shared(tile)), \"r\"(bytes) : \"memory\");\n"
+        "}\n"
+    )
+    with tempfile.TemporaryDirectory() as tmp:
+        cu = Path(tmp) / "probe.cu"
+        cu.write_text(src)
+        proc = subprocess.run([NVCC, *GENCODE, "-c", str(cu), "-o", str(Path(tmp) / "probe.o")],
+                              capture_output=True, text=True)
+        return proc.returncode == 0
+
+
+def _headers_mtime() -> float:
+    newest = 0.0
+    for pattern in ("include/msharp/*.h", "kernels/*.cuh"):
+        for h in CSRC.glob(pattern):
+            newest = max(newest, h.stat().st_mtime)
+    return newest
+
+
+def _compile_one(rel: str, extra: list[str], header_mtime: float, verbose: bool) -> Path:
+    src = CSRC / rel
+    obj = OBJ / (rel.replace("/", "_") + ".o")
+    if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, header_mtime):
+        return obj
+    obj.parent.mkdir(parents=True, exist_ok=True)
+    if rel.endswith(".cu"):
+        cmd = [NVCC, *NVCC_FLAGS, *INCLUDES, *extra, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = ["g++", *CXX_FLAGS, *INCLUDES, *extra, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print("  cc", rel, flush=True)
+    _run(cmd)
+    return obj
+
+
+def build_native(verbose: bool = False) -> dict[str, Path]:
+    """Build libmsharp.so, the benchmark binary and the C++ test runner. Returns their paths."""
+    OUT.mkdir(parents=True, exist_ok=True)
+    defines = ["-DMSHARP_HAS_BULK_MULTIMEM=%d" % (1 if probe_bulk_multimem() else 0)]
+    sources = list(LIB_SOURCES) + [s for s in OPTIONAL_LIB_SOURCES if (CSRC / s).exists()]
+    extra_units = ["app/main.cc"] + (["tests/test_main.cc"] if (CSRC / "tests/test_main.cc").exists() else [])
+    hm = _headers_mtime()
+    with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        futures = {rel: pool.submit(_compile_one, rel, defines, hm, verbose) for rel in sources + extra_units}
+        objs = {rel: f.result() for rel, f in futures.items()}
+
+    lib = OUT / "libmsharp.so"
+    lib_objs = [str(objs[s]) for s in sources]
+    link_tail = ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread"]
+    newest_obj = max(Path(o).stat().st_mtime for o in lib_objs)
+    if not lib.exists() or lib.stat().st_mtime < newest_obj:
+        _run(["g++", "-shared", "-o", str(lib), *lib_objs, *link_tail])
+    result = {"lib": lib}
+
+    exe = OUT / "mnnvl_sharp_allreduce"
+    if not exe.exists() or exe.stat().st_mtime < max(newest_obj, objs["app/main.cc"].stat().st_mtime):
+        _run(["g++", "-o", str(exe), str(objs["app/main.cc"]), *lib_objs, *link_tail])
+    result["exe"] = exe
+
+    if "tests/test_main.cc" in objs:
+        test_exe = OUT / "msharp_cpp_tests"
+        if not test_exe.exists() or test_exe.stat().st_mtime < max(newest_obj, objs["tests/test_main.cc"].stat().st_mtime):
+            _run(["g++", "-o", str(test_exe), str(objs["tests/test_main.cc"]), *lib_objs, *link_tail])
+        result["tests"] = test_exe
+    return result
+
+
+def build_torch_ops(verbose: bool = False) -> Path | None:
+    """Build the TORCH_LIBRARY operator library against the in-tree libmsharp.so."""
+    src = CSRC / "torch" / "ops.cpp"
+    if not src.exists():
+        return None
+    import torch
+    from torch.utils import cpp_extension
+
+    target = OUT / "msharp_torch_ops.so"
+    lib = OUT / "libmsharp.so"
+    if target.exists() and target.stat().st_mtime > max(src.stat().st_mtime, lib.stat().st_mtime, _headers_mtime()):
+        return target
+    includes = []
+    for inc in cpp_extension.include_paths():
+        includes += ["-isystem", inc]
+    import sysconfig
+
+    includes += ["-isystem", sysconfig.get_paths()["include"]]
+    torch_lib = Path(torch.__file__).parent / "lib"
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+           "-DTORCH_EXTENSION_NAME=msharp_torch_ops", *INCLUDES, *includes, str(src), "-o", str(target),
+           "-L", str(OUT), "-lmsharp", "-Wl,-rpath,$ORIGIN",
+           "-L", str(torch_lib), "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+           f"-Wl,-rpath,{torch_lib}"]
+    if verbose:
+        print("  cc torch/ops.cpp", flush=True)
+    _run(cmd)
+    return target
+
+
+def build_all(verbose: bool = False, with_torch: bool = True) -> dict[str, Path]:
+    result = build_native(verbose)
+    if with_torch:
+        ops = build_torch_ops(verbose)
+        if ops is not None:
+            result["torch_ops"] = ops
+    return result
+
+
+if __name__ == "__main__":
+    paths = build_all(verbose=True, with_torch="--no-torch" not in sys.argv)
+    for name, path in paths.items():
+        print(f"{name}: {path}")
