@@ -250,16 +250,17 @@ MSHARP_UNROLL
 }
 
 // Tagged pattern: value = ((element mod 61) - 30 + 3*rank) / 8 for 16-bit types (exact sums
-// that are never identically zero across ranks), and a small-exponent E4M3 code for FP8.
+// that are never identically zero across ranks); FP8 uses its own small-integer pattern below.
 MSHARP_HD float tagged_value(int rank, uint64_t element) {
   const int v = static_cast<int>(element % 61u) - 30 + 3 * (rank % 8);
   return static_cast<float>(v) * 0.125f;
 }
 
 MSHARP_HD uint8_t tagged_e4m3_byte(int rank, uint64_t element) {
-  // multiples of 2^-6 in [-7/64*4, ...]: keep every partial sum exact in fp16 and in E4M3 range.
-  const int v = static_cast<int>((element + 5u * static_cast<uint64_t>(rank)) % 15u) - 7;  // -7..7
-  return encode_e4m3(static_cast<float>(v) * 0.015625f);
+  // {-1, 0, 1, 2} / 16: the sum over up to 8 ranks is an integer in [-8, 16] sixteenths, which
+  // FP8 E4M3 represents exactly (four significant bits), so even the FP8 result is order-free.
+  const int v = static_cast<int>(counter_rng(0x7a67u, rank, element, 9) & 3u) - 1;
+  return encode_e4m3(static_cast<float>(v) * 0.0625f);
 }
 
 MSHARP_HD uint8_t pattern_e4m3_byte(int pattern, uint64_t seed, int rank, uint64_t element) {

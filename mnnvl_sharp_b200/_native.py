@@ -1,0 +1,140 @@
+"""ctypes binding of `libmsharp.so` (the C interface declared in csrc/include/msharp/c_api.h).
+
+The library is built in-tree by `mnnvl_sharp_b200._build`; importing this module builds it when it
+is missing. Errors from the library surface as `NativeError` with the library's own message.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_size_t, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmsharp.so"
+
+
+class NativeError(RuntimeError):
+    """An error reported by the native library."""
+
+
+def _load() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        from . import _build
+
+        _build.build_native()
+    return ctypes.CDLL(str(_LIB_PATH))
+
+
+lib = _load()
+
+_SIGNATURES = {
+    "msharp_last_error": (c_char_p, []),
+    "msharp_version": (c_char_p, []),
+    "msharp_encode": (c_int, [c_int, c_void_p, c_void_p, c_size_t]),
+    "msharp_decode": (c_int, [c_int, c_void_p, c_void_p, c_size_t]),
+    "msharp_generate": (c_int, [c_int, c_int, c_uint64, c_int, c_size_t, c_size_t, c_void_p]),
+    "msharp_reduce_f32": (c_int, [c_int, c_int, c_uint64, c_int, c_size_t, c_size_t, c_void_p]),
+    "msharp_reduce_f32_cast": (c_int, [c_int, c_int, c_uint64, c_int, c_size_t, c_size_t, c_void_p]),
+    "msharp_reduce_semantic": (c_int, [c_int, c_int, c_uint64, c_int, c_size_t, c_size_t, c_void_p]),
+    "msharp_reduce_arrays_f32": (c_int, [c_int, POINTER(c_void_p), c_int, c_size_t, c_void_p]),
+    "msharp_compare": (c_int, [c_int, c_int, c_uint64, c_int, c_void_p, c_size_t, POINTER(c_double)]),
+    "msharp_hash_words": (c_uint64, [c_void_p, c_size_t]),
+    "msharp_summarize": (c_int, [POINTER(c_double), c_size_t, POINTER(c_double)]),
+    "msharp_usage": (c_char_p, [c_char_p]),
+    "msharp_parse_config": (c_char_p, [c_int, POINTER(c_char_p)]),
+    "msharp_rack_from_yaml": (c_char_p, [c_char_p]),
+    "msharp_rack_from_file": (c_char_p, [c_char_p]),
+    "msharp_plan_from_yaml": (c_char_p, [c_char_p, c_int, c_char_p]),
+    "msharp_launch_texts": (c_char_p, [c_char_p, c_int, c_char_p, c_char_p, c_char_p, c_char_p]),
+    "msharp_parse_cpu_list": (c_char_p, [c_char_p]),
+    "msharp_yaml_to_json": (c_char_p, [c_char_p]),
+    "msharp_init_latency_csv_header": (c_char_p, []),
+    "msharp_run_cpu_only": (c_char_p, [c_int, POINTER(c_char_p)]),
+    "msharp_bootstrap_connect": (c_void_p, [c_int, c_int, c_char_p, c_int]),
+    "msharp_bootstrap_destroy": (None, [c_void_p]),
+    "msharp_bootstrap_barrier": (c_int, [c_void_p]),
+    "msharp_bootstrap_allgather": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
+    "msharp_bootstrap_broadcast": (c_int, [c_void_p, c_void_p, c_size_t, c_int]),
+    "msharp_bootstrap_allgather_fd": (c_int, [c_void_p, c_int, POINTER(c_int)]),
+    "msharp_bootstrap_abort": (c_int, [c_void_p, c_char_p]),
+    "msharp_fake_driver_reset": (None, [c_int]),
+    "msharp_fake_driver_set_attribute": (None, [c_int, c_int]),
+    "msharp_fake_driver_fail_call": (None, [c_char_p, c_int, c_int]),
+    "msharp_fake_driver_log": (c_char_p, []),
+    "msharp_fake_driver_leaks": (c_int, [POINTER(c_int)]),
+    "msharp_comm_create": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int]),
+    "msharp_comm_destroy": (c_int, [c_void_p]),
+    "msharp_comm_info": (c_char_p, [c_void_p]),
+    "msharp_comm_status": (c_int, [c_void_p, POINTER(c_uint32)]),
+    "msharp_comm_clear_status": (c_int, [c_void_p]),
+    "msharp_comm_reset": (c_int, [c_void_p]),
+    "msharp_comm_set_timeout_ms": (c_int, [c_void_p, c_int]),
+    "msharp_comm_set_multimem_barrier": (c_int, [c_void_p, c_int]),
+    "msharp_symm_alloc": (c_void_p, [c_void_p, c_size_t, c_int, c_int]),
+    "msharp_symm_free": (c_int, [c_void_p]),
+    "msharp_symm_info": (c_char_p, [c_void_p]),
+    "msharp_symm_input_ptr": (c_uint64, [c_void_p, c_int]),
+    "msharp_symm_output_ptr": (c_uint64, [c_void_p, c_int]),
+    "msharp_symm_mc_ptr": (c_uint64, [c_void_p]),
+    "msharp_symm_copy_to_host": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t]),
+    "msharp_symm_copy_from_host": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_size_t]),
+    "msharp_init_pattern": (c_int, [c_int, c_int, c_uint64, c_int, c_uint64, c_size_t, c_uint64]),
+    "msharp_poison_fill": (c_int, [c_uint64, c_size_t, c_uint64]),
+    "msharp_hash_device": (c_int, [c_uint64, c_size_t, c_uint64, c_uint64]),
+    "msharp_canary_check": (c_int, [c_void_p, c_void_p, c_uint64]),
+    "msharp_allreduce_pull": (c_int, [c_void_p, c_void_p, c_int, c_int, c_size_t, c_size_t, c_int, c_int, c_int, c_uint64]),
+    "msharp_allreduce_sw_f32": (c_int, [c_void_p, c_void_p, c_size_t, c_size_t, c_uint64, c_float, c_int, c_int, c_uint64]),
+    "msharp_allreduce_bulk_push": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int, c_uint64]),
+    "msharp_allreduce_reference_geometry": (c_int, [c_void_p, c_int, c_size_t, c_uint64]),
+    "msharp_bulk_multimem_compiled": (c_int, []),
+}
+
+for _name, (_res, _args) in _SIGNATURES.items():
+    _fn = getattr(lib, _name, None)
+    if _fn is not None:
+        _fn.restype = _res
+        _fn.argtypes = _args
+
+
+def declare(name: str, restype, argtypes) -> None:
+    """Declare the signature of an optional entry point (one that later additions export)."""
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+
+
+def last_error() -> str:
+    return (lib.msharp_last_error() or b"").decode()
+
+
+def check(rc: int) -> None:
+    """Raise NativeError if a status-returning native call failed."""
+    if rc != 0:
+        raise NativeError(last_error())
+
+
+def text(result: bytes | None) -> str:
+    """Return the string of a text-returning native call, or raise its error."""
+    if result is None:
+        raise NativeError(last_error())
+    return result.decode()
+
+
+def as_json(result: bytes | None):
+    return json.loads(text(result))
+
+
+def pointer(result: int | None) -> int:
+    """Return the handle of a pointer-returning native call, or raise its error."""
+    if not result:
+        raise NativeError(last_error())
+    return result
+
+
+def argv(args: list[str]):
+    arr = (c_char_p * len(args))(*[a.encode() for a in args])
+    return len(args), arr
+
+
+DTYPES = {"e4m3": 0, "f16": 1, "bf16": 2}
+PATTERNS = {"reference": 0, "seeded": 1, "tagged": 2}

@@ -1,0 +1,91 @@
+"""All-reduce (sum) on symmetric buffers. One kernel launch per rank; the kernel synchronises
+with its peers on the device, so nothing here blocks the host and the call composes with
+CUDA streams and graph capture.
+
+Backends (names as on the benchmark binary's command line):
+  legacy / pull  multimem.ld_reduce through the NVSwitch + multimem.st, every rank reducing
+                 1/world of the buffer (reference kernel: src/sharp_kernels.cu:108-120)
+  sw_f32         FP8 E4M3 with float32 accumulation and per-rank scales in registers
+  tma_async      bulk-async store-reduce push (reference kernel: src/sharp_kernels.cu:122-161)
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native as N
+from ..parallel.symmetric import Communicator, SymmetricBuffer
+
+_NATIVE_STREAM_OK = True
+
+
+def _stream() -> int:
+    return int(torch.cuda.current_stream().cuda_stream)
+
+
+def all_reduce_pull(comm: Communicator, buf: SymmetricBuffer, dtype: str, nbytes: int | None = None, offset: int = 0,
+                    acc_f32: bool | None = None, grid: int = 0, block: int = 0, unroll: int = 0) -> None:
+    """In place over the output region. dtype: 'e4m3' (fp16 accumulation in the switch), 'f16'
+    or 'bf16' (float32 accumulation by default, the element type with acc_f32=False)."""
+    if acc_f32 is None:
+        acc_f32 = dtype != "e4m3"
+    N.check(N.lib.msharp_allreduce_pull(comm.handle, buf.handle, N.DTYPES[dtype], 1 if acc_f32 else 0, offset,
+                                        buf.payload_bytes if nbytes is None else nbytes, grid, block, unroll, _stream()))
+
+
+def all_reduce_sw_f32(comm: Communicator, buf: SymmetricBuffer, nbytes: int | None = None, offset: int = 0,
+                      in_scales: torch.Tensor | None = None, out_scale: float = 1.0, grid: int = 0,
+                      block: int = 0) -> None:
+    """FP8 E4M3 in place: out = sat_e4m3(sum_r in_scales[r] * x_r / out_scale), float32 sum in
+    rank order. `in_scales` is a float32 CUDA tensor with one scale per rank (default all 1)."""
+    scales_ptr = 0
+    if in_scales is not None:
+        if in_scales.dtype != torch.float32 or not in_scales.is_cuda or in_scales.numel() < comm.world:
+            raise ValueError("in_scales must be a float32 CUDA tensor with one entry per rank")
+        scales_ptr = in_scales.data_ptr()
+    N.check(N.lib.msharp_allreduce_sw_f32(comm.handle, buf.handle, offset, buf.payload_bytes if nbytes is None else nbytes,
+                                          scales_ptr, 1.0 / out_scale, grid, block, _stream()))
+
+
+def all_reduce_bulk_push(comm: Communicator, buf: SymmetricBuffer, dtype: str = "f16", nbytes: int | None = None,
+                         offset: int = 0, grid: int = 0) -> None:
+    """Out of place (input region -> output region of an 'input_output' buffer), F16 or BF16."""
+    N.check(N.lib.msharp_allreduce_bulk_push(comm.handle, buf.handle, N.DTYPES[dtype], offset,
+                                             buf.payload_bytes if nbytes is None else nbytes, grid, _stream()))
+
+
+def all_reduce_reference_geometry(buf: SymmetricBuffer, dtype: str, nbytes: int) -> None:
+    """The reference project's launch shape (one rank, 4-byte operations, no device barrier).
+    The caller provides the host barriers and calls this on rank 0 only."""
+    N.check(N.lib.msharp_allreduce_reference_geometry(buf.handle, N.DTYPES[dtype], nbytes, _stream()))
+
+
+def all_reduce(comm: Communicator, buf: SymmetricBuffer, dtype: str, backend: str = "pull", **kwargs) -> None:
+    if backend in ("legacy", "pull"):
+        if backend == "legacy" and dtype != "e4m3":
+            raise ValueError("the legacy backend is FP8 E4M3 only")
+        all_reduce_pull(comm, buf, dtype, **kwargs)
+    elif backend == "sw_f32":
+        if dtype != "e4m3":
+            raise ValueError("the sw_f32 backend is FP8 E4M3 only")
+        all_reduce_sw_f32(comm, buf, **kwargs)
+    elif backend == "tma_async":
+        all_reduce_bulk_push(comm, buf, dtype, **kwargs)
+    else:
+        raise ValueError(f"unknown backend {backend!r}")
+
+
+def init_pattern(buf: SymmetricBuffer, dtype: str, pattern: str, rank: int, nbytes: int, seed: int = 2025,
+                 region: str = "input") -> None:
+    ptr = buf.input_ptr() if region == "input" else buf.output_ptr()
+    N.check(N.lib.msharp_init_pattern(N.DTYPES[dtype], N.PATTERNS[pattern], seed, rank, ptr, nbytes, _stream()))
+
+
+def poison_fill(ptr: int, nbytes: int) -> None:
+    N.check(N.lib.msharp_poison_fill(ptr, nbytes, _stream()))
+
+
+def device_hash(ptr: int, nbytes: int) -> int:
+    """Replica hash of `nbytes` at `ptr` (blocking)."""
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    N.check(N.lib.msharp_hash_device(ptr, nbytes, out.data_ptr(), _stream()))
+    return int(out.item()) & 0xFFFFFFFFFFFFFFFF

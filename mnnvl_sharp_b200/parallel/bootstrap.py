@@ -1,0 +1,88 @@
+"""Control plane between the rank processes of one host (Unix-socket hub in the native library).
+
+It does what MPI does for the reference project (handle exchange, barriers, small reductions;
+call sites listed in the reference at src/fabric_memory.cc:111-169 and src/main.cc:91-195) and
+can pass file descriptors between processes, which the POSIX-FD memory handles need.
+Every call is collective, has a deadline, and raises `NativeError` naming the rank that failed.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+from .. import _native as N
+
+
+class Bootstrap:
+    def __init__(self, rank: int, world: int, session: str = "default", timeout_ms: int = 30000):
+        self.rank = rank
+        self.world = world
+        self.session = session
+        self._h = N.pointer(N.lib.msharp_bootstrap_connect(rank, world, session.encode(), timeout_ms))
+
+    @classmethod
+    def from_env(cls, timeout_ms: int = 60000) -> "Bootstrap":
+        """RANK / WORLD_SIZE as set by torchrun or by this package's launcher; the session name
+        comes from MSHARP_SESSION, else from MASTER_PORT."""
+        rank = int(os.environ.get("RANK", "0"))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        session = os.environ.get("MSHARP_SESSION") or ("port" + os.environ.get("MASTER_PORT", "0"))
+        return cls(rank, world, session, timeout_ms)
+
+    @property
+    def handle(self) -> int:
+        return self._h
+
+    def barrier(self) -> None:
+        N.check(N.lib.msharp_bootstrap_barrier(self._h))
+
+    def allgather_bytes(self, payload: bytes) -> list[bytes]:
+        send = ctypes.create_string_buffer(payload, len(payload))
+        recv = ctypes.create_string_buffer(len(payload) * self.world)
+        N.check(N.lib.msharp_bootstrap_allgather(self._h, send, recv, len(payload)))
+        raw = recv.raw
+        return [raw[i * len(payload):(i + 1) * len(payload)] for i in range(self.world)]
+
+    def allgather_array(self, value: np.ndarray) -> np.ndarray:
+        value = np.ascontiguousarray(value)
+        out = np.empty((self.world,) + value.shape, dtype=value.dtype)
+        N.check(N.lib.msharp_bootstrap_allgather(self._h, value.ctypes.data, out.ctypes.data, value.nbytes))
+        return out
+
+    def allgather_float(self, value: float) -> list[float]:
+        return [float(v) for v in self.allgather_array(np.array([value], dtype=np.float64))[:, 0]]
+
+    def reduce_max(self, value: float) -> float:
+        return max(self.allgather_float(value))
+
+    def all_true(self, value: bool) -> bool:
+        return all(v != 0.0 for v in self.allgather_float(1.0 if value else 0.0))
+
+    def broadcast_bytes(self, payload: bytes, root: int = 0) -> bytes:
+        buf = ctypes.create_string_buffer(payload, len(payload))
+        N.check(N.lib.msharp_bootstrap_broadcast(self._h, buf, len(payload), root))
+        return buf.raw
+
+    def allgather_fd(self, fd: int) -> list[int]:
+        out = (ctypes.c_int * self.world)()
+        N.check(N.lib.msharp_bootstrap_allgather_fd(self._h, fd, out))
+        return list(out)
+
+    def abort(self, reason: str) -> None:
+        if self._h:
+            N.lib.msharp_bootstrap_abort(self._h, reason.encode())
+
+    def close(self) -> None:
+        if self._h:
+            N.lib.msharp_bootstrap_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc is not None:
+            self.abort(str(exc))
+        self.close()

@@ -1,0 +1,169 @@
+"""Communicator and symmetric buffers.
+
+A `Communicator` owns the per-process control block that kernels use to synchronise across
+GPUs; a `SymmetricBuffer` is the same-sized allocation on every rank, mapped on every rank at
+`slot(r)` and, when multicast is available, aliased by one multicast address. The reference
+project builds the same objects in src/fabric_memory.cc:72-171 and checks them with the canary
+test of src/main.cc:152-179.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+from dataclasses import dataclass
+
+import numpy as np
+
+from .. import _native as N
+from .bootstrap import Bootstrap
+
+HANDLE_TYPES = {"auto": 0, "posix_fd": 1, "fabric": 2}
+LAYOUTS = {"single": 0, "input_output": 1}
+
+STATUS_BITS = {
+    1: "entry_timeout",
+    2: "exit_timeout",
+    4: "copy_timeout",
+    8: "bad_argument",
+    16: "flag_timeout",
+    32: "canary_mismatch",
+}
+
+
+@dataclass
+class DeviceStatus:
+    bits: int
+    block: int
+    detail: int
+
+    @property
+    def ok(self) -> bool:
+        return self.bits == 0
+
+    def names(self) -> list[str]:
+        return [name for bit, name in STATUS_BITS.items() if self.bits & bit]
+
+
+class DeviceWaitError(RuntimeError):
+    """A kernel gave up waiting for a peer (or failed a self-check) and said so in its status."""
+
+    def __init__(self, what: str, status: DeviceStatus):
+        super().__init__(f"{what}: device status {status.names()} (block {status.block}, detail {status.detail})")
+        self.status = status
+
+
+class Communicator:
+    def __init__(self, bootstrap: Bootstrap, device: int, wait_timeout_ms: int = 2000, fake_driver: bool = False,
+                 handle_type: str = "auto"):
+        self.bootstrap = bootstrap
+        self.rank = bootstrap.rank
+        self.world = bootstrap.world
+        self.device = device
+        self.fake = fake_driver
+        self._h = N.pointer(N.lib.msharp_comm_create(bootstrap.handle, device, wait_timeout_ms, 1 if fake_driver else 0,
+                                                     HANDLE_TYPES[handle_type]))
+        self._buffers: list["SymmetricBuffer"] = []
+
+    @property
+    def handle(self) -> int:
+        return self._h
+
+    def info(self) -> dict:
+        return N.as_json(N.lib.msharp_comm_info(self._h))
+
+    def status(self) -> DeviceStatus:
+        out = (ctypes.c_uint32 * 3)()
+        N.check(N.lib.msharp_comm_status(self._h, out))
+        return DeviceStatus(int(out[0]), int(out[1]), int(out[2]))
+
+    def clear_status(self) -> None:
+        N.check(N.lib.msharp_comm_clear_status(self._h))
+
+    def raise_if_failed(self, what: str = "collective") -> None:
+        st = self.status()
+        if not st.ok:
+            raise DeviceWaitError(what, st)
+
+    def reset(self) -> None:
+        """Collective: bring the barrier counters of all ranks back in step after a timeout."""
+        N.check(N.lib.msharp_comm_reset(self._h))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        N.check(N.lib.msharp_comm_set_timeout_ms(self._h, ms))
+
+    def set_multimem_barrier(self, enabled: bool) -> None:
+        N.check(N.lib.msharp_comm_set_multimem_barrier(self._h, 1 if enabled else 0))
+
+    def alloc(self, payload_bytes: int, layout: str = "single", multicast: bool = True) -> "SymmetricBuffer":
+        buf = SymmetricBuffer(self, payload_bytes, layout, multicast)
+        self._buffers.append(buf)
+        return buf
+
+    def close(self) -> None:
+        """Collective: frees remaining buffers, then the control block."""
+        for buf in list(self._buffers):
+            buf.free()
+        if self._h:
+            N.check(N.lib.msharp_comm_destroy(self._h))
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        if exc is None:
+            self.close()
+
+
+class SymmetricBuffer:
+    def __init__(self, comm: Communicator, payload_bytes: int, layout: str, multicast: bool):
+        self.comm = comm
+        self.payload_bytes = payload_bytes
+        self._h = N.pointer(N.lib.msharp_symm_alloc(comm.handle, payload_bytes, LAYOUTS[layout], 1 if multicast else 0))
+        self.info = N.as_json(N.lib.msharp_symm_info(self._h))
+
+    @property
+    def handle(self) -> int:
+        return self._h
+
+    def input_ptr(self, rank: int | None = None) -> int:
+        return int(N.lib.msharp_symm_input_ptr(self._h, self.comm.rank if rank is None else rank))
+
+    def output_ptr(self, rank: int | None = None) -> int:
+        return int(N.lib.msharp_symm_output_ptr(self._h, self.comm.rank if rank is None else rank))
+
+    @property
+    def mc_ptr(self) -> int:
+        return int(N.lib.msharp_symm_mc_ptr(self._h))
+
+    def read(self, nbytes: int, offset: int = 0, slot_rank: int | None = None, region: str = "output") -> np.ndarray:
+        """Blocking copy to the host through the unicast mapping of `slot_rank` (default: own)."""
+        out = np.empty(nbytes, dtype=np.uint8)
+        base = self.info["output_offset"] if region == "output" else self.info["input_offset"]
+        N.check(N.lib.msharp_symm_copy_to_host(self._h, out.ctypes.data, self.comm.rank if slot_rank is None else slot_rank,
+                                               base + offset, nbytes))
+        return out
+
+    def write(self, data: np.ndarray, offset: int = 0, region: str = "input") -> None:
+        src = np.ascontiguousarray(data).view(np.uint8)
+        base = self.info["output_offset"] if region == "output" else self.info["input_offset"]
+        N.check(N.lib.msharp_symm_copy_from_host(self._h, self.comm.rank, base + offset, src.ctypes.data, src.nbytes))
+
+    def canary_check(self, stream: int = 0) -> None:
+        """Collective smoke test: every rank tags its slot, every rank reads every slot."""
+        N.check(N.lib.msharp_canary_check(self.comm.handle, self._h, stream))
+
+    def tensor(self, dtype, region: str = "output", rank: int | None = None, nbytes: int | None = None):
+        """A torch tensor viewing this buffer's memory on `rank` (default: own) without a copy."""
+        from .tensor_view import device_tensor
+
+        ptr = self.output_ptr(rank) if region == "output" else self.input_ptr(rank)
+        return device_tensor(ptr, self.payload_bytes if nbytes is None else nbytes, dtype, self.comm.device, owner=self)
+
+    def free(self) -> None:
+        """Collective."""
+        if self._h:
+            N.check(N.lib.msharp_symm_free(self._h))
+            self._h = None
+            if self in self.comm._buffers:
+                self.comm._buffers.remove(self)
