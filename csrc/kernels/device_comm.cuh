@@ -150,16 +150,16 @@ __device__ __forceinline__ bool wait_reach(const uint32_t* p, uint32_t target, u
 // CTA call it; returns false (for all threads) when a peer did not show up in time, in which
 // case the failure is recorded and the caller must not touch peer memory any more.
 //
-// Ordering: the caller's earlier global / multimem stores are made visible to all GPUs
-// (system-scope fence by every thread, then a CTA barrier) before the arrival is published;
-// after the wait, an acquire at system scope plus a CTA barrier orders later loads.
+// Ordering: a CTA barrier orders every thread's earlier global / multimem stores before the
+// publishing thread's release at system scope (release is cumulative over what the barrier
+// made visible to that thread), so peers that observe the arrival observe those stores; after
+// the wait, the acquire at system scope followed by a CTA barrier orders all later loads.
 __device__ __forceinline__ bool grid_peers_barrier(const DeviceComm& c, uint32_t failure_bit) {
   __shared__ int s_ok;
   if (c.world == 1) {
     __syncthreads();
     return true;
   }
-  __threadfence_system();
   __syncthreads();
   const unsigned slot = blockIdx.x;
   uint32_t* epochs = reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlEpochOffset);

@@ -168,10 +168,17 @@ void require_aligned(const void* p, std::size_t bytes, const char* what) {
 }  // namespace
 
 int device_sm_count() {
+  static int cached[64] = {0};
   int dev = 0;
-  int sms = 0;
   MSHARP_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] != 0) {
+    return cached[dev];
+  }
+  int sms = 0;
   MSHARP_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (dev >= 0 && dev < 64) {
+    cached[dev] = sms;
+  }
   return sms;
 }
 

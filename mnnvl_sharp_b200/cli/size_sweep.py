@@ -1,0 +1,129 @@
+"""Message-size sweep (powers of two from --min-bytes to --max-bytes) of this package's
+all-reduce backends and, with --nccl, of ncclAllReduce through torch.distributed for the same
+dtype and size, all device-timed as the maximum over ranks. One JSON line per point; rows are
+also appended to --csv as they are produced, and points already present there are skipped, so an
+interrupted sweep resumes where it stopped.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m mnnvl_sharp_b200.cli.size_sweep --nccl --csv gpurun_out/size_sweep.csv
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+
+import torch
+
+from .. import ops
+from ._common import busbw, init_rank, time_steps
+
+FIELDS = ["world", "impl", "backend", "dtype", "bytes", "ms", "algbw_gb_s", "busbw_gb_s", "timing"]
+
+
+def load_done(path: str) -> set[tuple]:
+    done = set()
+    if path and os.path.exists(path):
+        with open(path, newline="") as f:
+            for row in csv.DictReader(f):
+                done.add((int(row["world"]), row["impl"], row["backend"], row["dtype"], int(row["bytes"])))
+    return done
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--min-bytes", type=int, default=4096)
+    p.add_argument("--max-bytes", type=int, default=1 << 30)
+    p.add_argument("--cases", default="legacy:e4m3,pull:f16,sw_f32:e4m3,tma_async:f16")
+    p.add_argument("--nccl", action="store_true", help="also time ncclAllReduce (NVLS when NCCL picks it)")
+    p.add_argument("--csv", default="")
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--graph", action="store_true", help="time CUDA-graph replays (no host launch cost)")
+    args = p.parse_args()
+
+    boot, comm = init_rank()
+    world, rank = comm.world, comm.rank
+    sizes = []
+    s = args.min_bytes
+    while s <= args.max_bytes:
+        sizes.append(s)
+        s *= 2
+    done = load_done(args.csv) if rank == 0 else set()
+    writer = None
+    if rank == 0 and args.csv:
+        new = not os.path.exists(args.csv)
+        f = open(args.csv, "a", newline="")
+        writer = csv.DictWriter(f, fieldnames=FIELDS)
+        if new:
+            writer.writeheader()
+
+    def emit(row):
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+            if writer is not None:
+                writer.writerow(row)
+                f.flush()
+
+    def skip(key) -> bool:
+        # rank 0 decides (it owns the file); everyone follows
+        flag = boot.broadcast_bytes(b"\x01" if (rank == 0 and key in done) else b"\x00", 0)
+        return flag == b"\x01"
+
+    single = comm.alloc(args.max_bytes, layout="single")
+    double = None
+    for case in args.cases.split(","):
+        backend, dtype = case.split(":")
+        if backend == "tma_async" and double is None:
+            double = comm.alloc(args.max_bytes, layout="input_output", multicast=False)
+        buf = double if backend == "tma_async" else single
+        ops.init_pattern(buf, dtype, "seeded", rank, args.max_bytes)
+        for nbytes in sizes:
+            if backend == "tma_async" and nbytes > (256 << 20) and world > 4:
+                continue  # a push moves world x the bytes; the largest sizes add minutes, not insight
+            if skip((world, "ours", backend, dtype, nbytes)):
+                continue
+            iters = args.iters if nbytes >= (1 << 20) else args.iters * 5
+            ms = time_steps(boot, comm, lambda: ops.all_reduce(comm, buf, dtype, backend=backend, nbytes=nbytes), iters,
+                            graph=args.graph)
+            emit({"world": world, "impl": "ours", "backend": backend, "dtype": dtype, "bytes": nbytes, "ms": round(ms, 6),
+                  "algbw_gb_s": round(nbytes / (ms * 1e6), 3), "busbw_gb_s": round(busbw(nbytes, ms, world), 3),
+                  "timing": "graph" if args.graph else "launch"})
+
+    if args.nccl and world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        for dtype, tdtype in (("e4m3", getattr(torch, "float8_e4m3fn", None)), ("f16", torch.float16)):
+            if tdtype is None:
+                continue
+            nel = args.max_bytes // (1 if dtype == "e4m3" else 2)
+            try:
+                t = torch.zeros(nel, dtype=torch.float16 if dtype == "f16" else torch.uint8, device="cuda").view(tdtype)
+                dist.all_reduce(t[:16])
+                torch.cuda.synchronize()
+            except Exception as ex:  # torch may refuse float8 reductions
+                if rank == 0:
+                    print(json.dumps({"world": world, "impl": "nccl", "dtype": dtype,
+                                      "unsupported": f"{type(ex).__name__}: {ex}"[:200]}), flush=True)
+                continue
+            for nbytes in sizes:
+                if skip((world, "nccl", "nccl", dtype, nbytes)):
+                    continue
+                view = t[: nbytes // t.element_size()]
+                iters = args.iters if nbytes >= (1 << 20) else args.iters * 5
+                ms = time_steps(boot, comm, lambda: dist.all_reduce(view), iters, graph=args.graph)
+                emit({"world": world, "impl": "nccl", "backend": "nccl", "dtype": dtype, "bytes": nbytes, "ms": round(ms, 6),
+                      "algbw_gb_s": round(nbytes / (ms * 1e6), 3), "busbw_gb_s": round(busbw(nbytes, ms, world), 3),
+                  "timing": "graph" if args.graph else "launch"})
+        dist.destroy_process_group()
+
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.close()
+    boot.close()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

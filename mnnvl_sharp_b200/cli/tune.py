@@ -1,0 +1,55 @@
+"""Sweep launch shapes (grid, block, unroll) of the pull all-reduce and print one JSON line per
+shape, best last. Run one process per GPU, e.g.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m mnnvl_sharp_b200.cli.tune --bytes 1073741824 --dtype e4m3
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+
+from .. import ops
+from ._common import busbw, init_rank, time_steps
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--bytes", type=int, default=1 << 30)
+    p.add_argument("--dtype", default="e4m3", choices=["e4m3", "f16", "bf16"])
+    p.add_argument("--grids", default="16,32,64,148,296,444,592")
+    p.add_argument("--blocks", default="256,512,1024")
+    p.add_argument("--unrolls", default="1,2,4,8")
+    p.add_argument("--iters", type=int, default=8)
+    p.add_argument("--backend", default="pull", choices=["pull", "sw_f32", "tma_async"])
+    p.add_argument("--graph", action="store_true", help="time a CUDA-graph replay (no host launch cost)")
+    args = p.parse_args()
+
+    boot, comm = init_rank()
+    buf = comm.alloc(args.bytes, layout="input_output" if args.backend == "tma_async" else "single",
+                     multicast=args.backend != "tma_async")
+    ops.init_pattern(buf, args.dtype, "seeded", comm.rank, args.bytes)
+    rows = []
+    for grid, block, unroll in itertools.product([int(x) for x in args.grids.split(",")],
+                                                 [int(x) for x in args.blocks.split(",")],
+                                                 [int(x) for x in args.unrolls.split(",")]):
+        if args.backend == "pull":
+            fn = lambda: ops.all_reduce_pull(comm, buf, args.dtype, grid=grid, block=block, unroll=unroll)  # noqa: E731
+        elif args.backend == "sw_f32":
+            fn = lambda: ops.all_reduce_sw_f32(comm, buf, grid=grid, block=block)  # noqa: E731
+        else:
+            fn = lambda: ops.all_reduce_bulk_push(comm, buf, args.dtype, grid=grid)  # noqa: E731
+        ms = time_steps(boot, comm, fn, args.iters, warmup=2, graph=args.graph)
+        rows.append({"backend": args.backend, "dtype": args.dtype, "bytes": args.bytes, "grid": grid, "block": block, "unroll": unroll,
+                     "ms": round(ms, 5), "busbw_gb_s": round(busbw(args.bytes, ms, comm.world), 2)})
+    if comm.rank == 0:
+        for row in sorted(rows, key=lambda r: -r["ms"]):
+            print(json.dumps(row), flush=True)
+    comm.close()
+    boot.close()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
