@@ -46,9 +46,15 @@ struct State {
   std::map<std::string, int> counts;
 };
 
+void default_attributes(State& s);
+
 State& state() {
-  static State s;
-  return s;
+  static State* s = [] {
+    auto* fresh = new State();
+    default_attributes(*fresh);
+    return fresh;
+  }();
+  return *s;
 }
 
 constexpr size_t kGranularity = 2u << 20;
@@ -423,10 +429,7 @@ void default_attributes(State& s) {
 }  // namespace
 
 const DriverApi& fake_driver() {
-  static const DriverApi table = [] {
-    default_attributes(state());
-    return make_table();
-  }();
+  static const DriverApi table = make_table();
   return table;
 }
 
