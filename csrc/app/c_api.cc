@@ -14,6 +14,7 @@
 #include "msharp/comm_context.h"
 #include "msharp/config.h"
 #include "msharp/fake_driver.h"
+#include "msharp/gemm_allreduce.h"
 #include "msharp/json.h"
 #include "msharp/kernels.h"
 #include "msharp/oracle.h"
@@ -105,6 +106,7 @@ struct CommHandle {
   msharp::CapabilityInfo caps;
   msharp::SymmOptions base;
   std::unique_ptr<msharp::CommContext> ctx;
+  std::unique_ptr<msharp::SymmetricMemory> gemm_ws;
 };
 
 struct SymmHandle {
@@ -388,6 +390,10 @@ int msharp_comm_destroy(void* comm) {
       if (!handle->api->is_fake) {
         cudaDeviceSynchronize();
       }
+      if (handle->gemm_ws) {
+        handle->bootstrap->barrier();
+        handle->gemm_ws->destroy();
+      }
       handle->ctx->destroy(handle->bootstrap);
     }
   });
@@ -666,5 +672,59 @@ int msharp_allreduce_reference_geometry(void* symm, int dtype, size_t bytes, uin
 }
 
 int msharp_bulk_multimem_compiled(void) { return msharp::bulk_multimem_compiled() ? 1 : 0; }
+
+int msharp_gemm_workspace_init(void* comm) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    if (h->gemm_ws) {
+      return;
+    }
+    msharp::SymmOptions opt = h->base;
+    opt.payload_bytes = msharp::kGemmWsBytes;
+    opt.layout = msharp::RegionLayout::kSingle;
+    opt.want_multicast = false;  // arrivals are counted at the owner through unicast mappings
+    h->gemm_ws = msharp::SymmetricMemory::create(*h->api, *h->bootstrap, opt);
+    MSHARP_CUDA(cudaMemset(reinterpret_cast<void*>(h->gemm_ws->output_ptr(h->gemm_ws->rank())), 0, msharp::kGemmWsBytes));
+    MSHARP_CUDA(cudaDeviceSynchronize());
+    h->bootstrap->barrier();
+  });
+}
+
+int msharp_gemm_allreduce(void* comm, void* out_symm, uint64_t a, uint64_t a_scales, uint64_t w, uint64_t w_scales,
+                          int m, int n, int k, int reducer_ctas, uint64_t stream) {
+  return guarded([&] {
+    auto* h = static_cast<CommHandle*>(comm);
+    const msharp::SymmetricMemory& out = *static_cast<SymmHandle*>(out_symm)->mem;
+    if (static_cast<std::size_t>(m) * static_cast<std::size_t>(n) * 2 > out.payload_bytes) {
+      throw std::invalid_argument("gemm_allreduce: the output buffer is smaller than m * n BF16 values");
+    }
+    msharp::GemmAllReduceArgs args;
+    args.a = reinterpret_cast<const void*>(a);
+    args.a_scales = reinterpret_cast<const float*>(a_scales);
+    args.w = reinterpret_cast<const void*>(w);
+    args.w_scales = reinterpret_cast<const float*>(w_scales);
+    args.m = m;
+    args.n = n;
+    args.k = k;
+    args.out_local = reinterpret_cast<void*>(out.output_ptr(out.rank()));
+    args.reducer_ctas = reducer_ctas;
+    uint64_t peers[msharp::kMaxWorld] = {0};
+    if (out.world() > 1) {
+      if (out.mc_base == 0) {
+        throw std::runtime_error("gemm_allreduce: the output buffer has no multicast alias");
+      }
+      if (!h->gemm_ws) {
+        throw std::runtime_error("gemm_allreduce: call msharp_gemm_workspace_init first (collective)");
+      }
+      args.out_mc = reinterpret_cast<void*>(out.mc_output_ptr());
+      args.ws_local = reinterpret_cast<unsigned char*>(h->gemm_ws->output_ptr(out.rank()));
+      for (int r = 0; r < out.world(); ++r) {
+        peers[r] = static_cast<uint64_t>(h->gemm_ws->output_ptr(r));
+      }
+      args.ws_peers = peers;
+    }
+    msharp::launch_gemm_allreduce(*h->api, h->ctx->device(), args, as_stream(stream));
+  });
+}
 
 }  // extern "C"

@@ -56,6 +56,12 @@ struct DriverApi {
                                void** values) = nullptr;
   CUresult (*ModuleUnload)(CUmodule module) = nullptr;
 
+  CUresult (*TensorMapEncodeTiled)(CUtensorMap* map, CUtensorMapDataType type, cuuint32_t rank, void* address,
+                                   const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+                                   const cuuint32_t* element_strides, CUtensorMapInterleave interleave,
+                                   CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promotion,
+                                   CUtensorMapFloatOOBfill fill) = nullptr;
+
   bool is_fake = false;
 };
 

@@ -1,0 +1,55 @@
+// Row-parallel block-scaled FP8 GEMM fused with its all-reduce.
+//
+// Each rank holds a K-slice of a linear layer: A [M, K_local] FP8 E4M3 (row-major) with one
+// float scale per 1 x 128 block of K, and W [N, K_local] FP8 E4M3 (row-major, i.e. K-contiguous
+// like A) with one float scale per 128 x 128 block. The kernel computes this rank's partial
+// product on the tcgen05 tensor cores and, in the same launch, sums the partial products of all
+// ranks through the NVSwitch into a BF16 [M, N] result that ends up in every rank's copy of a
+// symmetric buffer. The reference project has no GEMM; this operation implements the fused
+// "compute then all-reduce" case that its in-switch reduction is meant for.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "msharp/device_comm.h"
+#include "msharp/driver_api.h"
+
+namespace msharp {
+
+constexpr int kGemmTileM = 128;
+constexpr int kGemmTileN = 128;
+constexpr int kGemmTileK = 128;       // one scale block along K
+constexpr int kGemmMaxTiles = 16384;  // flags in the workspace
+
+// Device workspace of the fused kernel: symmetric (every rank can address every rank's copy),
+// zero before the first launch; the kernel leaves it zero again.
+constexpr uint64_t kGemmWsFlagOffset = 0;  // u32[kGemmMaxTiles]: arrivals per output tile, counted at the tile's owner
+constexpr uint64_t kGemmWsBytes = 64ull << 10;
+
+struct GemmAllReduceArgs {
+  const void* a = nullptr;          // [M, K] e4m3
+  const float* a_scales = nullptr;  // [M, K/128]
+  const void* w = nullptr;          // [N, K] e4m3
+  const float* w_scales = nullptr;  // [N/128, K/128]
+  int m = 0;
+  int n = 0;
+  int k = 0;
+  // world > 1: `out_local` is this rank's copy of the symmetric BF16 [M, N] buffer and `out_mc`
+  // its multicast alias; `ws_local` is this rank's zero-initialised workspace (kGemmWsBytes) and
+  // `ws_peers` the unicast addresses of all ranks' workspaces. world == 1: those may be null.
+  void* out_local = nullptr;
+  void* out_mc = nullptr;
+  unsigned char* ws_local = nullptr;
+  const uint64_t* ws_peers = nullptr;  // host array [world]: workspace address of every rank as mapped here
+  int reducer_ctas = 0;  // 0 = default: how many CTAs also run reduction warps
+};
+
+// Enqueues the fused kernel. M and N must be multiples of 128, K a multiple of 128; pointers
+// 16-byte aligned. Throws std::runtime_error on bad arguments or a refused launch.
+void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const GemmAllReduceArgs& args,
+                           cudaStream_t stream);
+
+}  // namespace msharp

@@ -207,5 +207,60 @@ __device__ __forceinline__ bool grid_peers_barrier(const DeviceComm& c, uint32_t
   return ok;
 }
 
+// The same barrier for a group of warps inside a CTA (a named barrier instead of
+// __syncthreads): `tid` is the thread's index within the group of `nthreads` threads, `slot`
+// the barrier slot shared by the corresponding groups of all ranks.
+__device__ __forceinline__ bool group_peers_barrier(const DeviceComm& c, unsigned slot, int tid, int nthreads, int bar_id,
+                                                    int* s_ok, uint32_t failure_bit) {
+  auto sync = [&] { asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory"); };
+  if (c.world == 1) {
+    sync();
+    return true;
+  }
+  sync();
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlEpochOffset);
+  if (c.use_multimem_barrier) {
+    if (tid == 0) {
+      const uint32_t epoch = epochs[slot] + 1;
+      epochs[slot] = epoch;
+      uint32_t* mine = reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlCounterOffset) + slot;
+      uint32_t* all = reinterpret_cast<uint32_t*>(c.ctrl_mc + kCtrlCounterOffset) + slot;
+      multimem_red_release_add_u32(all, 1u);
+      const bool ok = wait_reach(mine, epoch * static_cast<uint32_t>(c.world), c.timeout_ns);
+      if (!ok) {
+        report(c, failure_bit, ld_acquire_sys(mine));
+      }
+      *s_ok = ok ? 1 : 0;
+    }
+  } else {
+    if (tid == 0) {
+      *s_ok = 1;
+    }
+    sync();
+    const uint32_t epoch = epochs[slot] + 1;
+    const uint64_t* table = reinterpret_cast<const uint64_t*>(c.ctrl_local + kCtrlPeerTableOffset);
+    for (int peer_rank = tid; peer_rank < c.world; peer_rank += nthreads) {
+      unsigned char* peer = reinterpret_cast<unsigned char*>(table[peer_rank]);
+      st_release_sys(reinterpret_cast<uint32_t*>(peer + kCtrlFlagOffset) + slot * kMaxWorld + c.rank, epoch);
+    }
+    for (int peer_rank = tid; peer_rank < c.world; peer_rank += nthreads) {
+      const uint32_t* mine =
+          reinterpret_cast<const uint32_t*>(c.ctrl_local + kCtrlFlagOffset) + slot * kMaxWorld + peer_rank;
+      if (!wait_reach(mine, epoch, c.timeout_ns)) {
+        report(c, failure_bit, peer_rank);
+        *s_ok = 0;
+      }
+    }
+    sync();
+    if (tid == 0) {
+      epochs[slot] = epochs[slot] + 1;
+    }
+  }
+  sync();
+  const bool ok = *s_ok != 0;
+  sync();
+  return ok;
+}
+
 }  // namespace dev
 }  // namespace msharp

@@ -1,0 +1,481 @@
+// Fused row-parallel block-scaled FP8 GEMM + all-reduce for sm_100a.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and W tiles (128 x 128 bytes
+//               each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
+//   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
+//               two TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
+//   warps 2-5   promotion + epilogue: tcgen05.ld of the 128-deep partial product, multiply by
+//               a_scale[row, kblock] * w_scale[ntile, kblock], accumulate in float32 registers
+//               (the float block scales are not the hardware's UE8M0 1x32 format, so the scaling
+//               cannot be left to the tensor core); after the last K block the BF16 row is stored
+//               to this rank's copy of the symmetric output and the tile's arrival is counted
+//               at the tile's owner with one release-add over NVLink
+//   warps 6-9   reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
+//               wait until every rank has published the tile, then multimem.ld_reduce (float32
+//               accumulation in the switch) + multimem.st the tile in place, so that the sum
+//               lands in every rank's copy while other tiles are still being multiplied
+// Every wait (mbarrier, flag, cross-GPU barrier) is bounded; on expiry the kernel records a
+// status bit, stops waiting, releases its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <stdexcept>
+#include <string>
+
+#include "device_comm.cuh"
+#include "msharp/gemm_allreduce.h"
+#include "msharp/kernels.h"
+
+namespace msharp {
+namespace {
+
+constexpr int BM = kGemmTileM;
+constexpr int BN = kGemmTileN;
+constexpr int BK = kGemmTileK;
+constexpr int kStages = 6;
+constexpr int kStageBytesA = BM * BK;  // FP8: one byte per element
+constexpr int kStageBytesB = BN * BK;
+constexpr int kUmmaK = 32;             // K extent of one kind::f8f6f4 instruction
+constexpr int kTmemCols = 256;         // two float32 accumulators of 128 columns
+constexpr int kThreads = 320;          // 10 warps
+constexpr int kEpilogueWarp0 = 2;
+constexpr int kReducerWarp0 = 6;
+constexpr int kSmemBytes = kStages * (kStageBytesA + kStageBytesB) + 1024;  // + alignment slack
+
+// ------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// Bounded wait for the phase with the given parity. Returns false when the deadline passed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns) {
+  const uint32_t addr = smem_addr(bar);
+  unsigned long long start = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) {
+      return true;
+    }
+    if ((spins & 255u) == 255u) {
+      const unsigned long long now = dev::global_timer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > timeout_ns) {
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_addr(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_result)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem]^T, FP8 inputs, float32 accumulate, issued by one thread.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit TMEM words: thread i of the warp gets lane (base + i), 32 columns.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __uint_as_float(r[i]);
+  }
+}
+
+// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (one swizzle span),
+// 128-byte swizzle, 8-row groups 1024 bytes apart. `byte_offset` selects the 32-byte K slice.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile, uint32_t byte_offset) {
+  const uint32_t addr = smem_addr(tile) + byte_offset;
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);        // start address
+  desc |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (unused with swizzle)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  desc |= static_cast<uint64_t>(1) << 46;                        // descriptor version of this architecture
+  desc |= static_cast<uint64_t>(2) << 61;                        // 128-byte swizzle
+  return desc;
+}
+
+// Instruction descriptor: float32 accumulator, E4M3 x E4M3, both operands K-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+struct GemmParams {
+  const float* a_scales;
+  const float* w_scales;
+  int m, n, k;
+  __nv_bfloat16* out_local;
+  __nv_bfloat16* out_mc;
+  unsigned char* ws_local;
+  PeerPointers ws_peers;  // workspace of every rank (unicast mappings); used when world > 1
+  int reducer_ctas;
+};
+
+template <bool MULTI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const GemmParams p, const DeviceComm comm) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* smem_a = smem;
+  unsigned char* smem_b = smem + kStages * kStageBytesA;
+
+  __shared__ __align__(8) uint64_t bar_full[kStages];
+  __shared__ __align__(8) uint64_t bar_empty[kStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ volatile int s_abort;
+  __shared__ int s_barrier_ok;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_n = p.n / BN;
+  const int total_tiles = (p.m / BM) * tiles_n;
+  const int k_blocks = p.k / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bar_acc_full[b], 1);
+      mbar_init(&bar_acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem_base, kTmemCols);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * BM;
+        const int n0 = (t % tiles_n) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          if (!mbar_wait(&bar_empty[s], phase ^ 1u, comm.timeout_ns)) {
+            dev::report(comm, kStatusCopyTimeout, 0x100u + s);
+            s_abort = 1;
+            break;
+          }
+          mbar_expect_tx(&bar_full[s], kStageBytesA + kStageBytesB);
+          tma_load_2d(smem_a + s * kStageBytesA, &map_a, kb * BK, m0, &bar_full[s]);
+          tma_load_2d(smem_b + s * kStageBytesB, &map_w, kb * BK, n0, &bar_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(BM, BN);
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          const int buf = it & 1;
+          const uint32_t acc_phase = (it >> 1) & 1u;
+          if (!mbar_wait(&bar_acc_empty[buf], acc_phase ^ 1u, comm.timeout_ns) ||
+              !mbar_wait(&bar_full[s], phase, comm.timeout_ns)) {
+            dev::report(comm, kStatusCopyTimeout, 0x200u + s);
+            s_abort = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * BN);
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            umma_f8(acc, umma_desc_sw128(smem_a + s * kStageBytesA, k * kUmmaK),
+                    umma_desc_sw128(smem_b + s * kStageBytesB, k * kUmmaK), idesc, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&bar_empty[s]);       // the stage may be refilled once these MMAs have read it
+          umma_commit(&bar_acc_full[buf]);  // and the 128-deep partial product is ready for promotion
+        }
+        if (s_abort) {
+          break;
+        }
+      }
+    }
+  } else if (warp < kReducerWarp0) {
+    // ------------------------------------------------------------------ promotion + epilogue
+    const int quarter = warp & 3;  // the TMEM lanes a warp may touch are fixed by its index mod 4
+    const int row_in_tile = quarter * 32 + lane;
+    const int etid = (warp - kEpilogueWarp0) * 32 + lane;
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
+      const int mt = t / tiles_n;
+      const int nt = t % tiles_n;
+      const int row = mt * BM + row_in_tile;
+      const float* a_scale_row = p.a_scales + static_cast<size_t>(row) * k_blocks;
+      const float* w_scale_row = p.w_scales + static_cast<size_t>(nt) * k_blocks;
+      float acc[BN];
+#pragma unroll
+      for (int j = 0; j < BN; ++j) {
+        acc[j] = 0.0f;
+      }
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        const float scale = __ldg(a_scale_row + kb) * __ldg(w_scale_row + kb);
+        if (!mbar_wait(&bar_acc_full[buf], acc_phase, comm.timeout_ns)) {
+          dev::report(comm, kStatusCopyTimeout, 0x300u + buf);
+          s_abort = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          float v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            acc[c * 32 + j] = fmaf(scale, v[j], acc[c * 32 + j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bar_acc_empty[buf]);
+        }
+      }
+      if (!ok) {
+        break;
+      }
+      // BF16 row of this tile into this rank's copy of the output (the partial product when
+      // several ranks take part, the final result otherwise)
+      uint4* dst = reinterpret_cast<uint4*>(p.out_local + static_cast<size_t>(row) * p.n + static_cast<size_t>(nt) * BN);
+#pragma unroll
+      for (int q = 0; q < BN / 8; ++q) {
+        uint4 v;
+        v.x = pack_bf16(acc[q * 8 + 0], acc[q * 8 + 1]);
+        v.y = pack_bf16(acc[q * 8 + 2], acc[q * 8 + 3]);
+        v.z = pack_bf16(acc[q * 8 + 4], acc[q * 8 + 5]);
+        v.w = pack_bf16(acc[q * 8 + 6], acc[q * 8 + 7]);
+        dst[q] = v;
+      }
+      if constexpr (MULTI) {
+        // all 128 rows are stored, then one release-add tells the owner of the tile
+        named_barrier(1, 128);
+        if (etid == 0) {
+          const int owner = t % comm.world;
+          uint32_t* flag = reinterpret_cast<uint32_t*>(p.ws_peers.ptr[owner] + kGemmWsFlagOffset) + t;
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ reducers
+    if constexpr (MULTI) {
+      const int rtid = (warp - kReducerWarp0) * 32 + lane;
+      if (static_cast<int>(blockIdx.x) < p.reducer_ctas) {
+        // peers may only start writing sums into this rank's output once its earlier work is done
+        bool ok = dev::group_peers_barrier(comm, blockIdx.x, rtid, 128, 2, &s_barrier_ok, kStatusEntryTimeout);
+        dev::fence_proxy_alias();
+        uint32_t* flags = reinterpret_cast<uint32_t*>(p.ws_local + kGemmWsFlagOffset);
+        const uint32_t want = static_cast<uint32_t>(comm.world);
+        // owned tiles are t = rank, rank + world, ...; the j-th of them goes to reducer CTA j mod reducer_ctas
+        for (int j = blockIdx.x; ok && !s_abort; j += p.reducer_ctas) {
+          const long long t = static_cast<long long>(j) * comm.world + comm.rank;
+          if (t >= total_tiles) {
+            break;
+          }
+          if (rtid == 0) {
+            const bool arrived = dev::wait_reach(flags + t, want, comm.timeout_ns);
+            if (!arrived) {
+              dev::report(comm, kStatusFlagTimeout, static_cast<uint32_t>(t));
+              s_abort = 1;
+            } else {
+              flags[t] = 0;  // re-armed for the next launch (no peer signals it again before the closing barrier)
+            }
+          }
+          named_barrier(3, 128);
+          if (s_abort) {
+            break;
+          }
+          const int mt = static_cast<int>(t) / tiles_n;
+          const int nt = static_cast<int>(t) % tiles_n;
+          // 128 rows x 256 bytes: 16 vectors per row; thread -> (row, vector) with rows interleaved
+          __nv_bfloat16* tile_mc = p.out_mc + static_cast<size_t>(mt) * BM * p.n + static_cast<size_t>(nt) * BN;
+#pragma unroll 1
+          for (int base = 0; base < BM * 16; base += 128 * 4) {
+            dev::Vec4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int idx = base + u * 128 + rtid;
+              const int r = idx >> 4;
+              const int c = idx & 15;
+              v[u] = dev::ld_reduce_v4<dev::kReduceBF16AccF32>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(r) * p.n) + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int idx = base + u * 128 + rtid;
+              const int r = idx >> 4;
+              const int c = idx & 15;
+              dev::st_all_v4<false>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(r) * p.n) + c, v[u]);
+            }
+          }
+        }
+        dev::fence_proxy_alias();
+        dev::group_peers_barrier(comm, blockIdx.x, rtid, 128, 2, &s_barrier_ok, kStatusExitTimeout);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+CUtensorMap make_tile_map(const DriverApi& api, const void* base, int rows, int cols_k) {
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols_k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols_k)};  // bytes between rows (FP8: one byte per element)
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(BM)};
+  const cuuint32_t elem[2] = {1, 1};
+  check_driver(api,
+               api.TensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                                        elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+               "cuTensorMapEncodeTiled");
+  return map;
+}
+
+}  // namespace
+
+void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const GemmAllReduceArgs& a, cudaStream_t stream) {
+  auto aligned = [](const void* ptr) { return ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.m % BM != 0 || a.n % BN != 0 || a.k % BK != 0) {
+    throw std::runtime_error("gemm_allreduce: M and N must be positive multiples of 128 and K a positive multiple of 128");
+  }
+  if (!aligned(a.a) || !aligned(a.w) || !aligned(a.out_local) || a.a_scales == nullptr || a.w_scales == nullptr) {
+    throw std::runtime_error("gemm_allreduce: operands must be non-null and 16-byte aligned");
+  }
+  const long long tiles = static_cast<long long>(a.m / BM) * (a.n / BN);
+  if (tiles > kGemmMaxTiles) {
+    throw std::runtime_error("gemm_allreduce: more than " + std::to_string(kGemmMaxTiles) + " output tiles");
+  }
+  const bool multi = comm.world > 1;
+  if (multi && (a.out_mc == nullptr || a.ws_local == nullptr)) {
+    throw std::runtime_error("gemm_allreduce: several ranks need the multicast alias of the output and a workspace");
+  }
+  GemmParams p{};
+  p.a_scales = a.a_scales;
+  p.w_scales = a.w_scales;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.out_local = static_cast<__nv_bfloat16*>(a.out_local);
+  p.out_mc = static_cast<__nv_bfloat16*>(a.out_mc);
+  p.ws_local = a.ws_local;
+  for (int r = 0; r < comm.world && r < kMaxWorld; ++r) {
+    p.ws_peers.ptr[r] = a.ws_peers != nullptr ? a.ws_peers[r] : 0;
+    if (multi && p.ws_peers.ptr[r] == 0) {
+      throw std::runtime_error("gemm_allreduce: workspace address of rank " + std::to_string(r) + " is missing");
+    }
+  }
+  const int sms = device_sm_count();
+  // The grid is always one CTA per SM so that the reducer CTAs (which wait for their peers) are
+  // resident and so that the same barrier slots are used by every launch.
+  const int grid = sms;
+  p.reducer_ctas = std::min(grid, a.reducer_ctas > 0 ? a.reducer_ctas : 32);
+
+  const CUtensorMap map_a = make_tile_map(api, a.a, a.m, a.k);
+  const CUtensorMap map_w = make_tile_map(api, a.w, a.n, a.k);
+  auto launch = [&](auto kernel) {
+    static bool configured[64] = {false};
+    int device = 0;
+    MSHARP_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64 || !configured[device]) {
+      MSHARP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+      if (device >= 0 && device < 64) {
+        configured[device] = true;
+      }
+    }
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, p, comm);
+  };
+  if (multi) {
+    launch(gemm_allreduce_kernel<true>);
+  } else {
+    launch(gemm_allreduce_kernel<false>);
+  }
+  const cudaError_t err = cudaPeekAtLastError();
+  if (err != cudaSuccess) {
+    throw std::runtime_error(std::string("gemm_allreduce_kernel launch failed: ") + cudaGetErrorString(err));
+  }
+}
+
+}  // namespace msharp
