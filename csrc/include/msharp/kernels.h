@@ -68,5 +68,7 @@ void launch_allreduce_bulk_push(const DeviceComm& comm, Dtype dtype, const void*
 bool bulk_multimem_compiled();  // whether this build contains the multimem bulk form
 
 int device_sm_count();
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device); cheap afterwards.
+void ensure_max_dynamic_smem(const void* kernel, int bytes);
 
 }  // namespace msharp

@@ -558,15 +558,7 @@ void launch_allreduce_bulk_push(const DeviceComm& comm, Dtype dtype, const void*
   const std::size_t smem = static_cast<std::size_t>(kBulkStages) * kBulkTileBytes;
   const std::size_t tiles = (bytes + kBulkTileBytes - 1) / kBulkTileBytes;
   auto go = [&](auto kernel) {
-    static bool configured[64] = {false};  // per kernel (one lambda instantiation each) and device
-    int device = 0;
-    MSHARP_CUDA(cudaGetDevice(&device));
-    if (device < 0 || device >= 64 || !configured[device]) {
-      MSHARP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-      if (device >= 0 && device < 64) {
-        configured[device] = true;
-      }
-    }
+    ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel), static_cast<int>(smem));
     const int grid = resident_grid(kernel, kBulkThreads, smem, tiles, shape.grid);
     kernel<<<grid, kBulkThreads, smem, stream>>>(comm, static_cast<const unsigned char*>(local_input), outputs, bytes);
   };

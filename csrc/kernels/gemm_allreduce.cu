@@ -5,13 +5,14 @@
 //               each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
 //               two TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
-//   warps 2-5   promotion + epilogue: tcgen05.ld of the 128-deep partial product, multiply by
+//   warps 2-9   promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
+//               tcgen05.ld of the 128-deep partial product, multiply by
 //               a_scale[row, kblock] * w_scale[ntile, kblock], accumulate in float32 registers
 //               (the float block scales are not the hardware's UE8M0 1x32 format, so the scaling
 //               cannot be left to the tensor core); after the last K block the BF16 row is stored
 //               to this rank's copy of the symmetric output and the tile's arrival is counted
 //               at the tile's owner with one release-add over NVLink
-//   warps 6-9   reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
+//   warps 10-13 reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
 //               wait until every rank has published the tile, then multimem.ld_reduce (float32
 //               accumulation in the switch) + multimem.st the tile in place, so that the sum
 //               lands in every rank's copy while other tiles are still being multiplied
@@ -40,9 +41,11 @@ constexpr int kStageBytesA = BM * BK;  // FP8: one byte per element
 constexpr int kStageBytesB = BN * BK;
 constexpr int kUmmaK = 32;             // K extent of one kind::f8f6f4 instruction
 constexpr int kTmemCols = 256;         // two float32 accumulators of 128 columns
-constexpr int kThreads = 320;          // 10 warps
+constexpr int kThreads = 448;          // 14 warps
 constexpr int kEpilogueWarp0 = 2;
-constexpr int kReducerWarp0 = 6;
+constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter, each taking half of the columns
+constexpr int kEpilogueCols = BN / 2;
+constexpr int kReducerWarp0 = kEpilogueWarp0 + kEpilogueWarps;
 constexpr int kSmemBytes = kStages * (kStageBytesA + kStageBytesB) + 1024;  // + alignment slack
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -112,8 +115,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 // 32 lanes x 32 columns of 32-bit TMEM words: thread i of the warp gets lane (base + i), 32 columns.
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+// Issue only (no wait): the caller overlaps several loads and waits once.
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -122,12 +125,9 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float* v) {
                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    v[i] = __uint_as_float(r[i]);
-  }
 }
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (one swizzle span),
 // 128-byte swizzle, 8-row groups 1024 bytes apart. `byte_offset` selects the 32-byte K slice.
@@ -198,7 +198,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bar_acc_full[b], 1);
-      mbar_init(&bar_acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&bar_acc_empty[b], kEpilogueWarps);  // one arrival per epilogue warp
     }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -267,6 +267,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp < kReducerWarp0) {
     // ------------------------------------------------------------------ promotion + epilogue
     const int quarter = warp & 3;  // the TMEM lanes a warp may touch are fixed by its index mod 4
+    const int half = (warp - kEpilogueWarp0) >> 2;  // which 64 columns of the tile
     const int row_in_tile = quarter * 32 + lane;
     const int etid = (warp - kEpilogueWarp0) * 32 + lane;
     uint32_t it = 0;
@@ -276,16 +277,21 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int row = mt * BM + row_in_tile;
       const float* a_scale_row = p.a_scales + static_cast<size_t>(row) * k_blocks;
       const float* w_scale_row = p.w_scales + static_cast<size_t>(nt) * k_blocks;
-      float acc[BN];
+      float acc[kEpilogueCols];
 #pragma unroll
-      for (int j = 0; j < BN; ++j) {
+      for (int j = 0; j < kEpilogueCols; ++j) {
         acc[j] = 0.0f;
       }
       bool ok = true;
+      // the scale of the next K block is fetched while the current one is being accumulated
+      float next_scale = __ldg(a_scale_row) * __ldg(w_scale_row);
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        const float scale = __ldg(a_scale_row + kb) * __ldg(w_scale_row + kb);
+        const float scale = next_scale;
+        if (kb + 1 < k_blocks) {
+          next_scale = __ldg(a_scale_row + kb + 1) * __ldg(w_scale_row + kb + 1);
+        }
         if (!mbar_wait(&bar_acc_full[buf], acc_phase, comm.timeout_ns)) {
           dev::report(comm, kStatusCopyTimeout, 0x300u + buf);
           s_abort = 1;
@@ -293,30 +299,32 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * BN);
-#pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          float v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            acc[c * 32 + j] = fmaf(scale, v[j], acc[c * 32 + j]);
-          }
-        }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               static_cast<uint32_t>(buf * BN + half * kEpilogueCols);
+        uint32_t v[kEpilogueCols];
+        tmem_ld_32x32_issue(taddr, v);
+        tmem_ld_32x32_issue(taddr + 32, v + 32);
+        tmem_ld_wait();
+        // the accumulator buffer is free as soon as its values are in registers
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&bar_acc_empty[buf]);
         }
+#pragma unroll
+        for (int j = 0; j < kEpilogueCols; ++j) {
+          acc[j] = fmaf(scale, __uint_as_float(v[j]), acc[j]);
+        }
       }
       if (!ok) {
         break;
       }
-      // BF16 row of this tile into this rank's copy of the output (the partial product when
+      // BF16 half-row of this tile into this rank's copy of the output (the partial product when
       // several ranks take part, the final result otherwise)
-      uint4* dst = reinterpret_cast<uint4*>(p.out_local + static_cast<size_t>(row) * p.n + static_cast<size_t>(nt) * BN);
+      uint4* dst = reinterpret_cast<uint4*>(p.out_local + static_cast<size_t>(row) * p.n + static_cast<size_t>(nt) * BN +
+                                            half * kEpilogueCols);
 #pragma unroll
-      for (int q = 0; q < BN / 8; ++q) {
+      for (int q = 0; q < kEpilogueCols / 8; ++q) {
         uint4 v;
         v.x = pack_bf16(acc[q * 8 + 0], acc[q * 8 + 1]);
         v.y = pack_bf16(acc[q * 8 + 2], acc[q * 8 + 3]);
@@ -325,8 +333,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         dst[q] = v;
       }
       if constexpr (MULTI) {
-        // all 128 rows are stored, then one release-add tells the owner of the tile
-        named_barrier(1, 128);
+        // the whole tile is stored, then one release-add tells the owner of the tile
+        named_barrier(1, kEpilogueWarps * 32);
         if (etid == 0) {
           const int owner = t % comm.world;
           uint32_t* flag = reinterpret_cast<uint32_t*>(p.ws_peers.ptr[owner] + kGemmWsFlagOffset) + t;
@@ -456,15 +464,7 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
   const CUtensorMap map_a = make_tile_map(api, a.a, a.m, a.k);
   const CUtensorMap map_w = make_tile_map(api, a.w, a.n, a.k);
   auto launch = [&](auto kernel) {
-    static bool configured[64] = {false};
-    int device = 0;
-    MSHARP_CUDA(cudaGetDevice(&device));
-    if (device < 0 || device >= 64 || !configured[device]) {
-      MSHARP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-      if (device >= 0 && device < 64) {
-        configured[device] = true;
-      }
-    }
+    ensure_max_dynamic_smem(reinterpret_cast<const void*>(kernel), kSmemBytes);
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_w, p, comm);
   };
   if (multi) {

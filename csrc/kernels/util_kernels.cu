@@ -1,7 +1,10 @@
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <set>
 #include <stdexcept>
 #include <string>
+#include <utility>
 
 #include "device_comm.cuh"
 #include "msharp/kernels.h"
@@ -180,6 +183,19 @@ int device_sm_count() {
     cached[dev] = sms;
   }
   return sms;
+}
+
+void ensure_max_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int device = 0;
+  MSHARP_CUDA(cudaGetDevice(&device));
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, device}) != 0) {
+    return;
+  }
+  MSHARP_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  done.insert({kernel, device});
 }
 
 void launch_init_pattern(Dtype dtype, int pattern, uint64_t seed, int rank, void* dst, std::size_t bytes,

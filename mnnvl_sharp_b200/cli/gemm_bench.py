@@ -1,0 +1,115 @@
+"""Times the fused block-scaled FP8 GEMM + all-reduce against the unfused baseline made of
+library calls (cuBLASLt FP8 GEMM through torch._scaled_mm, then ncclAllReduce), on the shape of
+a Llama-70B FFN down-projection split over the ranks (per rank A [8192, 3584], W [8192, 3584]).
+One process per GPU; one JSON line from rank 0, with the fraction of the roofline reached:
+the slower of FLOPs at the measured BF16 GEMM peak doubled for FP8 (no FP8 peak is measured)
+and the bytes that must cross NVLink at the measured 770 GB/s per direction.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m mnnvl_sharp_b200.cli.gemm_bench
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import ops
+from ._common import init_rank, time_steps
+
+LINK_GB_S = 770.0  # measured peer copy, per direction per GPU
+
+
+def measured_bf16_tflops() -> tuple[float, str]:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--m", type=int, default=8192)
+    p.add_argument("--n", type=int, default=8192)
+    p.add_argument("--k-local", type=int, default=3584)
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--reducer-ctas", type=int, default=0)
+    p.add_argument("--no-baseline", action="store_true")
+    p.add_argument("--graph", action="store_true")
+    args = p.parse_args()
+
+    boot, comm = init_rank()
+    world, rank = comm.world, comm.rank
+    m, n, k = args.m, args.n, args.k_local
+    torch.manual_seed(100 + rank)
+    k_total = k * world
+    a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda") / k_total ** 0.5, 1)
+    w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda") / k_total ** 0.5, 128)
+    op = ops.GemmAllReduce(comm, m, n)
+
+    # correctness on a corner of the output: float32 reference of every rank's partial, summed on the host side
+    out = op(a, sa, w, sw)
+    torch.cuda.synchronize()
+    comm.raise_if_failed("gemm_allreduce")
+    rows = slice(0, 256)
+    part = (ops.dequantize_blockwise(a[rows], sa[rows], 1) @ ops.dequantize_blockwise(w[:512], sw[:4], 128).t()).cpu().numpy()
+    total = boot.allgather_array(part).sum(axis=0)
+    got = out[rows, :512].float().cpu().numpy()
+    max_err = float(abs(got - total).max())
+    ref_max = float(abs(total).max())
+
+    fused_ms = time_steps(boot, comm, lambda: op(a, sa, w, sw, reducer_ctas=args.reducer_ctas), args.iters, graph=args.graph)
+    flops = 2.0 * m * n * k
+    peak, peak_kind = measured_bf16_tflops()
+    compute_ms = flops / (2.0 * peak * 1e12) * 1e3
+    out_bytes = m * n * 2
+    link_ms = out_bytes * (1.0 + 1.0 / world) / (LINK_GB_S * 1e9) * 1e3 if world > 1 else 0.0
+    roof_ms = max(compute_ms, link_ms)
+    row = {"op": "gemm_allreduce_fp8_blockscaled", "world": world, "m": m, "n": n, "k_local": k,
+           "fused_ms": round(fused_ms, 4), "tflops_per_gpu": round(flops / fused_ms / 1e9, 1),
+           "roofline_ms": round(roof_ms, 4), "roofline_bound": "nvlink" if link_ms > compute_ms else "tensor",
+           "roofline_fraction": round(roof_ms / fused_ms, 3), "peak_source": f"2 x bf16 {peak_kind} ({peak} TFLOP/s)",
+           "max_abs_err": max_err, "ref_abs_max": ref_max}
+
+    if not args.no_baseline:
+        # unfused library baseline: per-tensor-scaled FP8 GEMM (cuBLASLt) to BF16, then NCCL all-reduce
+        one = torch.ones((), device="cuda")
+        wt = w.t()  # column-major view as _scaled_mm expects
+        base_out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+
+        def cublas():
+            torch._scaled_mm(a, wt, scale_a=one, scale_b=one, out_dtype=torch.bfloat16, out=base_out)
+
+        try:
+            row["cublas_fp8_gemm_ms"] = round(time_steps(boot, comm, cublas, args.iters, graph=args.graph), 4)
+        except Exception as ex:  # noqa: BLE001
+            row["cublas_fp8_gemm_ms"] = None
+            row["cublas_note"] = f"{type(ex).__name__}: {ex}"[:160]
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+
+            def unfused():
+                cublas()
+                dist.all_reduce(base_out)
+
+            row["nccl_allreduce_ms"] = round(time_steps(boot, comm, lambda: dist.all_reduce(base_out), args.iters,
+                                                        graph=args.graph), 4)
+            if row.get("cublas_fp8_gemm_ms") is not None:
+                row["unfused_ms"] = round(time_steps(boot, comm, unfused, args.iters, graph=args.graph), 4)
+                row["speedup_vs_unfused"] = round(row["unfused_ms"] / fused_ms, 3)
+            dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(row), flush=True)
+    op.free()
+    comm.close()
+    boot.close()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,170 @@
+"""One rank of a multi-GPU test case (started by tests/test_gpu_multi.py)."""
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+
+from mnnvl_sharp_b200 import ops
+from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+from mnnvl_sharp_b200.utils import numerics as nm
+
+
+def check_allreduce(comm, boot, backend, dtype, pattern, nbytes, layout="single", multicast=True, **kw):
+    buf = comm.alloc(nbytes, layout=layout, multicast=multicast)
+    buf.canary_check()
+    ops.poison_fill(buf.output_ptr(), nbytes)
+    ops.init_pattern(buf, dtype, pattern, comm.rank, nbytes)
+    torch.cuda.synchronize()
+    boot.barrier()
+    ops.all_reduce(comm, buf, dtype, backend=backend, **kw)
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.raise_if_failed(backend)
+    got = buf.read(nbytes).view(nm.storage_dtype(dtype))
+    m = nm.compare(dtype, pattern, comm.world, got)
+    hashes = boot.allgather_array(np.array([ops.device_hash(buf.output_ptr(), nbytes)], dtype=np.uint64))[:, 0]
+    buf.free()
+    return m, len(set(int(h) for h in hashes)) == 1
+
+
+def case_allreduce_exact(comm, boot):
+    ok = True
+    detail = []
+    for backend, dtype, layout, mc in [("legacy", "e4m3", "single", True), ("pull", "f16", "single", True),
+                                       ("pull", "bf16", "single", True), ("sw_f32", "e4m3", "single", True),
+                                       ("sw_f32", "e4m3", "single", False), ("tma_async", "f16", "input_output", False),
+                                       ("tma_async", "bf16", "input_output", False)]:
+        for nbytes in (16, 4096 + 16, 1 << 20, (3 << 20) + 48):
+            if backend != "tma_async" and nbytes == 16:
+                nbytes = 20  # sizes that are multiples of 4 but not of 16 exercise the tail path
+            m, same = check_allreduce(comm, boot, backend, dtype, "tagged", nbytes, layout, mc)
+            good = same and m.exact_mismatches == 0
+            detail.append((backend, dtype, nbytes, m.exact_mismatches, same))
+            ok = ok and good
+    return {"ok": ok, "detail": [d for d in detail if d[3] or not d[4]]}
+
+
+def case_allreduce_seeded(comm, boot):
+    ok = True
+    detail = []
+    for backend, dtype, layout, mc, tol in [("legacy", "e4m3", "single", True, 1), ("pull", "f16", "single", True, 1),
+                                            ("pull", "bf16", "single", True, 1), ("sw_f32", "e4m3", "single", True, 0),
+                                            ("tma_async", "f16", "input_output", False, comm.world)]:
+        m, same = check_allreduce(comm, boot, backend, dtype, "seeded", 8 << 20, layout, mc)
+        good = same and m.max_requantized_ulp_distance <= tol and m.switch_model_mismatches == 0 if dtype == "e4m3" and backend == "legacy" \
+            else same and m.max_requantized_ulp_distance <= tol
+        detail.append((backend, dtype, m.max_requantized_ulp_distance, m.switch_model_mismatches, same))
+        ok = ok and good
+    return {"ok": ok, "detail": detail}
+
+
+def case_allreduce_flag_barrier(comm, boot):
+    comm.set_multimem_barrier(False)  # plain peer stores for the barrier instead of multimem.red
+    m, same = check_allreduce(comm, boot, "sw_f32", "e4m3", "seeded", 4 << 20, multicast=False)
+    m2, same2 = check_allreduce(comm, boot, "pull", "f16", "tagged", 4 << 20)
+    return {"ok": same and same2 and m.requantized_mismatches == 0 and m2.exact_mismatches == 0}
+
+
+def case_gemm_allreduce(comm, boot):
+    ok = True
+    detail = []
+    for (m, n, k) in [(256, 256, 512), (1024, 768, 1024), (2048, 2048, 3584)]:
+        torch.manual_seed(11 + comm.rank)
+        k_total = k * comm.world
+        a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda") / k_total ** 0.5, 1)
+        w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda") / k_total ** 0.5, 128)
+        op = ops.GemmAllReduce(comm, m, n)
+        for rep in range(3):  # repeated launches reuse (and must re-arm) the tile flags
+            op.out.fill_(float("nan"))
+            torch.cuda.synchronize()
+            boot.barrier()
+            out = op(a, sa, w, sw)
+            torch.cuda.synchronize()
+            boot.barrier()
+            comm.raise_if_failed("gemm_allreduce")
+        part = ops.reference_fp32(a, sa, w, sw).cpu().numpy()
+        total = boot.allgather_array(part).sum(axis=0)
+        got = out.float().cpu().numpy()
+        err = float(np.abs(got - total).max())
+        ref = float(np.abs(total).max())
+        hashes = boot.allgather_array(np.array([ops.device_hash(op.out_buf.output_ptr(), m * n * 2)], dtype=np.uint64))[:, 0]
+        same = len(set(int(h) for h in hashes)) == 1
+        good = same and not np.isnan(got).any() and err <= ref * 2 ** -6 + 1e-3
+        detail.append((m, n, k, err, ref, same))
+        ok = ok and good
+        op.free()
+    return {"ok": ok, "detail": detail}
+
+
+def case_absent_peer(comm, boot):
+    """Rank 1 sits this launch out. Rank 0's kernel waits 200 ms for it, then returns with a status."""
+    buf = comm.alloc(1 << 20)
+    comm.set_multimem_barrier(False)  # plain peer stores: no multicast traffic while a peer is idle
+    comm.set_timeout_ms(200)
+    boot.barrier()
+    out = {"role": "idle", "ok": True}
+    if comm.rank == 0:
+        t0 = time.time()
+        ops.all_reduce_sw_f32(comm, buf)
+        torch.cuda.synchronize()
+        elapsed = (time.time() - t0) * 1e3
+        st = comm.status()
+        x = torch.ones(16, device="cuda").sum().item()  # the context still works
+        out = {"role": "waiter", "ok": True, "status_names": st.names(), "elapsed_ms": elapsed, "context_ok_after": x == 16.0}
+    boot.barrier()
+    comm.set_timeout_ms(2000)
+    comm.reset()  # collective: counters of both ranks back in step
+    ops.init_pattern(buf, "e4m3", "tagged", comm.rank, 1 << 20)
+    torch.cuda.synchronize()
+    boot.barrier()
+    ops.all_reduce_sw_f32(comm, buf)
+    torch.cuda.synchronize()
+    boot.barrier()
+    m = nm.compare("e4m3", "tagged", comm.world, buf.read(1 << 20))
+    out["recovered"] = comm.status().ok and m.exact_mismatches == 0
+    buf.free()
+    return out
+
+
+def case_rank_leaves(comm, boot):
+    """Rank 1 leaves after two steps, between steps, with nothing in flight; rank 0 learns of it on
+    the host before launching anything else."""
+    buf = comm.alloc(1 << 20)
+    comm.set_multimem_barrier(False)
+    steps = 0
+    error = ""
+    try:
+        for step in range(4):
+            if comm.rank == 1 and step == 2:
+                torch.cuda.synchronize()
+                print(json.dumps({"role": "leaver", "ok": True}), flush=True)
+                os._exit(0)
+            boot.barrier()  # host agreement before every launch: a missing rank shows up here
+            ops.all_reduce_sw_f32(comm, buf)
+            torch.cuda.synchronize()
+            steps += 1
+    except Exception as ex:  # noqa: BLE001
+        error = str(ex)
+    print(json.dumps({"role": "stayer", "ok": True, "steps_done": steps, "error": error}), flush=True)
+    os._exit(0)  # the peer's mappings are gone; skip collective teardown
+
+
+def main():
+    case = sys.argv[1]
+    rank = int(os.environ["RANK"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    boot = Bootstrap.from_env(timeout_ms=30000 if case != "rank_leaves" else 5000)
+    comm = Communicator(boot, int(os.environ["LOCAL_RANK"]))
+    result = globals()["case_" + case](comm, boot)
+    print(json.dumps(result), flush=True)
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.close()
+    boot.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+"""The fused block-scaled FP8 GEMM kernel against a plain float32 PyTorch reference (one GPU)."""
+import os
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def comm():
+    import torch
+
+    from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+
+    torch.cuda.set_device(0)
+    boot = Bootstrap(0, 1, session=f"tg{os.getpid()}")
+    c = Communicator(boot, 0)
+    yield c
+    c.close()
+    boot.close()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 256, 384), (384, 128, 1024), (1024, 2048, 3584),
+                                   (19 * 128, 17 * 128, 7 * 128)])
+def test_gemm_matches_fp32_reference(comm, m, n, k):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    torch.manual_seed(m + n + k)
+    a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda") / k ** 0.5, 1)
+    w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda") / k ** 0.5, 128)
+    # uneven scales exercise the per-block promotion (uniform scales would hide a wrong block index)
+    sa = (sa * (1.0 + torch.rand_like(sa))).contiguous()
+    sw = (sw * (1.0 + torch.rand_like(sw))).contiguous()
+    op = ops.GemmAllReduce(comm, m, n)
+    op.out.fill_(float("nan"))
+    out = op(a, sa, w, sw).float()
+    torch.cuda.synchronize()
+    comm.raise_if_failed("gemm")
+    ref = ops.reference_fp32(a, sa, w, sw)
+    assert not torch.isnan(out).any()
+    # BF16 output: relative 2^-8 of the value plus float32 accumulation-order noise
+    tol = ref.abs() * 2 ** -7 + ref.abs().max() * 1e-3
+    assert ((out - ref).abs() <= tol).all(), float((out - ref).abs().max())
+    op.free()
+
+
+def test_gemm_rejects_bad_shapes(comm):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    with pytest.raises(ValueError):
+        ops.GemmAllReduce(comm, 100, 128)
+    op = ops.GemmAllReduce(comm, 128, 128)
+    a = torch.zeros(128, 64, device="cuda").to(torch.float8_e4m3fn)
+    with pytest.raises(ValueError):
+        op(a, torch.ones(128, 1, device="cuda"), a, torch.ones(1, 1, device="cuda"))
+    op.free()
+
+
+def test_repeated_launches_and_graph_replay(comm):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    m = n = 512
+    k = 1024
+    torch.manual_seed(3)
+    a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda") / k ** 0.5, 1)
+    w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda") / k ** 0.5, 128)
+    op = ops.GemmAllReduce(comm, m, n)
+    ref = ops.reference_fp32(a, sa, w, sw)
+    for _ in range(3):
+        op(a, sa, w, sw)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        op(a, sa, w, sw)
+    op.out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    comm.raise_if_failed("gemm")
+    assert ((op.out.float() - ref).abs() <= ref.abs() * 2 ** -7 + ref.abs().max() * 1e-3).all()
+    op.free()

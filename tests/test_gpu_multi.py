@@ -1,0 +1,83 @@
+"""Multi-GPU tests: every test starts one process per GPU on this host (2 GPUs, or as many as
+MSHARP_TEST_WORLD asks for and the box has) and checks results against the host oracle."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpus() -> int:
+    try:
+        import torch
+
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _world() -> int:
+    return min(_gpus(), int(os.environ.get("MSHARP_TEST_WORLD", "2")))
+
+
+needs_two = pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+
+
+def run_workers(case: str, world: int, timeout: int = 300, extra_env=None):
+    env = dict(os.environ)
+    env.update({"MSHARP_SESSION": f"mt{os.getpid()}_{case}", "WORLD_SIZE": str(world), "PYTHONPATH": ROOT,
+                "NCCL_NVLS_ENABLE": "0"})
+    env.update(extra_env or {})
+    procs = []
+    for rank in range(world):
+        e = dict(env, RANK=str(rank), LOCAL_RANK=str(rank))
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "multi_worker.py"), case],
+                                      env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, err = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, err = p.communicate()
+            err += "\n[killed: timeout]"
+        outs.append((p.returncode, out, err))
+    return outs
+
+
+def results_of(outs):
+    rows = []
+    for rc, out, err in outs:
+        assert rc == 0, f"worker failed (rc={rc}):\n{out}\n{err[-3000:]}"
+        rows.append(json.loads(out.strip().splitlines()[-1]))
+    return rows
+
+
+@needs_two
+@pytest.mark.parametrize("case", ["allreduce_exact", "allreduce_seeded", "allreduce_flag_barrier", "gemm_allreduce"])
+def test_multi_gpu_case(case):
+    rows = results_of(run_workers(case, _world()))
+    for r in rows:
+        assert r["ok"], r
+
+
+@needs_two
+def test_absent_peer_is_reported_not_hung():
+    """One rank never launches: the other's kernel gives up after its short deadline, says so in
+    its status word, and the process carries on (no trap, no hang, context still usable)."""
+    rows = results_of(run_workers("absent_peer", 2))
+    waiting = [r for r in rows if r["role"] == "waiter"][0]
+    assert waiting["status_names"] == ["entry_timeout"] and waiting["elapsed_ms"] < 2000
+    assert waiting["context_ok_after"] and waiting["recovered"]
+
+
+@needs_two
+def test_rank_leaving_between_steps_is_noticed_on_the_host():
+    outs = run_workers("rank_leaves", 2)
+    rows = [json.loads(o.strip().splitlines()[-1]) for rc, o, e in outs if o.strip()]
+    stayer = [r for r in rows if r["role"] == "stayer"][0]
+    assert stayer["steps_done"] == 2 and "rank 1" in stayer["error"]
