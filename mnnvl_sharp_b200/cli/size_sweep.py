@@ -72,7 +72,7 @@ def main() -> int:
 
     single = comm.alloc(args.max_bytes, layout="single")
     double = None
-    for case in args.cases.split(","):
+    for case in ([] if args.cases in ("", "none") else args.cases.split(",")):
         backend, dtype = case.split(":")
         if backend == "tma_async" and double is None:
             double = comm.alloc(args.max_bytes, layout="input_output", multicast=False)
