@@ -49,6 +49,9 @@ int final_status(const RunReport& r) {
   if (!r.has_results) {
     return 0;
   }
+  if (r.cfg.pattern == "seeded" && r.tolerance_abs > 0.0) {
+    return r.within_tolerance ? 0 : 2;
+  }
   if (!hashes_match(r.hashes)) {
     return 2;
   }
@@ -134,6 +137,7 @@ std::string json_report(const RunReport& r) {
   if (r.has_results) {
     w.key("switch_model_exact_mismatches").value(static_cast<uint64_t>(r.metrics.switch_model_mismatches));
     w.key("tolerance_ulp").value(r.tolerance_ulp);
+    w.key("tolerance_abs").value(r.tolerance_abs);
     w.key("within_tolerance").value(r.within_tolerance);
     w.key("algbw_gb_s").value(algbw_gb_s(r.cfg.bytes, r.device_ms.median));
     w.key("busbw_gb_s").value(busbw_gb_s(r.cfg.bytes, r.device_ms.median, n));

@@ -37,6 +37,10 @@ struct RunReport {
   std::string bulk_variant;  // "multimem", "unicast_fanout" or "" (not a bulk run)
   std::string kernel_variant;
   int tolerance_ulp = 0;
+  // > 0: the result is judged by absolute error instead (push backends on inexact inputs: every
+  // replica adds in its own arrival order, so replicas may differ in the last bits and a distance
+  // in representable values means nothing for sums that cancel to almost zero)
+  double tolerance_abs = 0.0;
   bool within_tolerance = true;
   int grid = 0;
   int block = 0;

@@ -1,0 +1,248 @@
+// Native unit tests of the host-side library (no GPU): run `msharp_cpp_tests`; exit code 0 = pass.
+// They cover what is easier to state in C++ than through the C interface: the JSON / human
+// report writers (key order of the reference project's src/main.cc:295-354), the CSV row,
+// align_up overflow handling, topology validation messages, and the device-status texts.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <iostream>
+#include <limits>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "msharp/comm_context.h"
+#include "msharp/config.h"
+#include "msharp/json.h"
+#include "msharp/numerics.h"
+#include "msharp/oracle.h"
+#include "msharp/rack.h"
+#include "msharp/report.h"
+#include "msharp/symm_mem.h"
+#include "msharp/topology.h"
+
+namespace {
+
+int g_failures = 0;
+
+#define EXPECT(cond)                                                                  \
+  do {                                                                                \
+    if (!(cond)) {                                                                    \
+      std::printf("FAIL %s:%d: %s\n", __FILE__, __LINE__, #cond);                     \
+      ++g_failures;                                                                   \
+    }                                                                                 \
+  } while (0)
+
+bool throws_with(const std::function<void()>& fn, const std::string& needle) {
+  try {
+    fn();
+  } catch (const std::exception& ex) {
+    return std::string(ex.what()).find(needle) != std::string::npos;
+  }
+  return false;
+}
+
+std::size_t find_key(const std::string& json, const std::string& key) { return json.find("\"" + key + "\":"); }
+
+msharp::RunReport sample_report(bool with_results) {
+  using namespace msharp;
+  RunReport r;
+  r.cfg = parse_config({"prog", "--rack-config", "r.yaml", "--json"});
+  r.cfg.init_only = !with_results;
+  r.caps.sharp_e4m3_supported = true;
+  r.caps.sharp_tma_async_supported = true;
+  for (int i = 0; i < 2; ++i) {
+    RankMappingRecord rec;
+    rec.world_rank = i;
+    rec.local_rank = i;
+    rec.gpu_ordinal = i;
+    rec.host_numa_id = 0;
+    std::snprintf(rec.host_label, sizeof(rec.host_label), "tray\"a");
+    std::snprintf(rec.os_hostname, sizeof(rec.os_hostname), "vm");
+    r.records.push_back(rec);
+  }
+  r.allocation_bytes = 1073741824;
+  r.multicast_bytes = 1073741824;
+  r.peer_init = summarize({4.5, 4.0});
+  r.peer_init_by_rank = {4.5, 4.0};
+  r.handle_kind = "posix_fd";
+  if (with_results) {
+    r.has_results = true;
+    r.hashes = {0xabcdef12ull, 0xabcdef12ull};
+    r.metrics.max_abs_error = 0.015625f;
+    r.device_ms = summarize({2.0, 2.5, 2.25});
+    r.wall_ms = summarize({2.1, 2.6, 2.3});
+  }
+  return r;
+}
+
+void test_json_report() {
+  using namespace msharp;
+  const std::string keys[] = {"selected_rank_count", "rank_selection", "sharp_backend", "datatype", "init_only",
+                              "payload_bytes", "allocation_bytes", "input_offset", "output_offset", "multicast_bytes",
+                              "datatype_support", "host_mapping", "peer_init_ms", "peer_init_min_ms", "peer_init_median_ms",
+                              "peer_init_p95_ms", "peer_init_max_ms", "peer_init_local_ms_by_rank", "hashes_match", "hashes",
+                              "semantic_exact_mismatches", "f32_requantized_mismatches", "f32_max_requantized_ulp_distance",
+                              "f32_max_abs_error", "f32_mean_abs_error", "sharp_kernel_ms", "collective_wall_ms"};
+  for (bool with_results : {false, true}) {
+    const std::string j = json_report(sample_report(with_results));
+    std::size_t last = 0;
+    for (const auto& k : keys) {
+      const std::size_t at = find_key(j, k);
+      EXPECT(at != std::string::npos);
+      EXPECT(at >= last);  // the reference's key order
+      last = at;
+    }
+    EXPECT(j.front() == '{' && j.back() == '}' && j.find('\n') == std::string::npos);
+    EXPECT(j.find("\"nvfp4\":\"unsupported\",\"mxfp4\":\"unsupported\"") != std::string::npos);
+    EXPECT(j.find("\"host_label\":\"tray\\\"a\"") != std::string::npos);  // escaped
+    EXPECT(j.find("\"peer_init_ms\":4.5,\"peer_init_min_ms\":4,\"peer_init_median_ms\":4.5") != std::string::npos);
+    if (with_results) {
+      EXPECT(j.find("\"hashes_match\":true,\"hashes\":[\"abcdef12\",\"abcdef12\"]") != std::string::npos);
+      EXPECT(j.find("\"f32_max_abs_error\":0.015625") != std::string::npos);
+      EXPECT(j.find("\"sharp_kernel_ms\":{\"min\":2,\"median\":2.25,\"p95\":2.5,\"max\":2.5}") != std::string::npos);
+      EXPECT(find_key(j, "busbw_gb_s") > find_key(j, "collective_wall_ms"));  // extensions come last
+    } else {
+      EXPECT(j.find("\"hashes_match\":null,\"hashes\":[],\"semantic_exact_mismatches\":null") != std::string::npos);
+      EXPECT(j.find("\"f32_mean_abs_error\":null") != std::string::npos);
+    }
+  }
+}
+
+void test_human_report_and_status() {
+  using namespace msharp;
+  RunReport r = sample_report(true);
+  const std::string h = human_report(r);
+  EXPECT(h.rfind("mnnvl_sharp_allreduce\n  selected_rank_count: 2\n", 0) == 0);
+  EXPECT(h.find("  peer_init_ms: min=4.000 median=4.500 p95=4.500 max=4.500\n  smoke_test: passed\n") != std::string::npos);
+  EXPECT(h.find("  replica_hashes: 0xabcdef12 0xabcdef12\n  hashes_match: true\n") != std::string::npos);
+  EXPECT(h.find("effective_logical_bandwidth_gib_s_median") != std::string::npos);
+  r.has_results = false;
+  EXPECT(human_report(r).find("  sharp_allreduce: skipped\n") != std::string::npos);
+
+  r = sample_report(true);
+  EXPECT(final_status(r) == 0);
+  r.metrics.exact_mismatches = 3;  // in-switch FP8 is judged by the bracketing rule, not by RNE equality
+  EXPECT(final_status(r) == 0);
+  r.metrics.switch_model_mismatches = 1;
+  EXPECT(final_status(r) == 2);
+  r.metrics.switch_model_mismatches = 0;
+  r.hashes[1] ^= 1;
+  EXPECT(final_status(r) == 2);
+  r = sample_report(true);
+  r.cfg.sharp_backend = Backend::kSwF32;
+  r.metrics.exact_mismatches = 1;
+  EXPECT(final_status(r) == 2);
+  r.cfg.pattern = "seeded";
+  r.within_tolerance = true;
+  EXPECT(final_status(r) == 0);
+  r.within_tolerance = false;
+  EXPECT(final_status(r) == 2);
+  r.tolerance_abs = 0.1;  // push backends on inexact inputs: replicas may differ, the error bound decides
+  r.within_tolerance = true;
+  r.hashes[1] ^= 1;
+  EXPECT(final_status(r) == 0);
+}
+
+void test_bandwidth_and_csv() {
+  using namespace msharp;
+  EXPECT(std::fabs(algbw_gb_s(1000000000, 1.0) - 1000.0) < 1e-9);
+  EXPECT(std::fabs(busbw_gb_s(1000000000, 1.0, 8) - 1750.0) < 1e-9);
+  EXPECT(busbw_gb_s(1000000000, 1.0, 1) == 0.0);
+  EXPECT(std::fabs(logical_gib_s(1073741824, 1000.0, 8) - 8.0) < 1e-9);
+  EXPECT(algbw_gb_s(1, 0.0) == 0.0);
+  EXPECT(std::string(kInitLatencyCsvHeader) ==
+         "rank_count,repeat,sharp_backend,peer_init_ms,peer_init_min_ms,peer_init_median_ms,peer_init_p95_ms,peer_init_max_ms");
+  EXPECT(init_latency_csv_row(8, 1, "legacy", 4.5, 4, 4.25, 4.5, 4.5) == "8,1,legacy,4.5,4,4.25,4.5,4.5");
+}
+
+void test_align_up_and_json_writer() {
+  using namespace msharp;
+  EXPECT(align_up(1, 2097152) == 2097152 && align_up(2097152, 2097152) == 2097152 && align_up(0, 8) == 0);
+  EXPECT(throws_with([] { align_up(5, 0); }, "alignment cannot be zero"));
+  EXPECT(throws_with([] { align_up(std::numeric_limits<std::size_t>::max() - 2, 16); }, "overflows"));
+  JsonWriter w;
+  w.begin_object().key("a").value(1).key("b").begin_array().value("x\ny").value(true).null().end_array().key("c").value(
+      std::nan(""));
+  w.end_object();
+  EXPECT(w.str() == "{\"a\":1,\"b\":[\"x\\ny\",true,null],\"c\":null}");
+  EXPECT(json_escape("tab\t\"q\"\\") == "tab\\t\\\"q\\\"\\\\");
+}
+
+void test_topology_validation() {
+  using namespace msharp;
+  const RackConfig rack = RackConfig::parse(
+      "rack:\n  - a:\n      hostname: x\n      device: [0, 1]\n  - b:\n      hostname: y\n      device: [2, 3]\n");
+  const RankPlan plan = build_rank_plan(rack, 4, "balanced");  // a0 b2 a1 b3
+  auto rec = [](int rank, int local, int rack_index, int gpu, const char* host, int numa = 0) {
+    RankMappingRecord r;
+    r.world_rank = rank;
+    r.local_rank = local;
+    r.rack_index = rack_index;
+    r.gpu_ordinal = gpu;
+    r.host_numa_id = numa;
+    std::snprintf(r.host_label, sizeof(r.host_label), "%s", host);
+    return r;
+  };
+  std::vector<RankMappingRecord> good = {rec(0, 0, 0, 0, "a"), rec(1, 0, 1, 2, "b"), rec(2, 1, 0, 1, "a"), rec(3, 1, 1, 3, "b")};
+  validate_rank_mappings(good, rack, plan);
+  auto bad = good;
+  bad[1] = rec(1, 0, 1, 3, "b");
+  EXPECT(throws_with([&] { validate_rank_mappings(bad, rack, plan); }, "rank 1 GPU ordinal does not match"));
+  bad = good;
+  bad[2] = rec(2, 1, 1, 1, "a");
+  EXPECT(throws_with([&] { validate_rank_mappings(bad, rack, plan); }, "rank 2 rack index does not match"));
+  bad = good;
+  bad[3] = rec(3, 1, 1, 3, "b", -1);
+  EXPECT(throws_with([&] { validate_rank_mappings(bad, rack, plan); }, "did not resolve a valid HOST_NUMA_ID"));
+  bad = good;
+  bad[3] = rec(2, 1, 0, 1, "a");
+  EXPECT(throws_with([&] { validate_rank_mappings(bad, rack, plan); }, "duplicate world rank"));
+  bad = good;
+  bad.pop_back();
+  EXPECT(throws_with([&] { validate_rank_mappings(bad, rack, plan); }, "record count does not match"));
+  EXPECT(throws_with([&] { discover_rank_info(0, 3, rack, plan, "a"); }, "world_size 3 does not match selected rank_count 4"));
+  EXPECT(throws_with([&] { discover_rank_info(0, 4, rack, plan, "zzz"); }, "did not match rack.yaml"));
+  EXPECT(throws_with([&] { discover_rank_info(1, 4, rack, plan, "a"); }, "selected rank plan expects 'b'"));
+  const RankInfo info = discover_rank_info(2, 4, rack, plan, "a.domain");
+  EXPECT(info.local_rank == 1 && info.local_size == 2 && info.gpu_ordinal == 1 && info.rack_index == 0 && info.rack_count == 2);
+  EXPECT(throws_with([] { pin_thread_to_numa(-1); }, "HOST_NUMA_ID is unavailable"));
+  EXPECT(throws_with([] { pin_thread_to_numa(9999); }, "could not read"));
+}
+
+void test_status_text() {
+  using namespace msharp;
+  EXPECT(describe_status(DeviceStatus{0, 0, 0}) == "ok");
+  const std::string s = describe_status(DeviceStatus{kStatusEntryTimeout | kStatusCanaryMismatch, 7, (3u << 8) | 5u});
+  EXPECT(s.find("opening barrier") != std::string::npos && s.find("slot 3, word 5") != std::string::npos &&
+         s.find("block 7") != std::string::npos);
+}
+
+void test_codec_spot_checks() {
+  using namespace msharp;
+  EXPECT(encode_e4m3(448.0f) == 0x7e && encode_e4m3(1e30f) == 0x7e && encode_e4m3(-1e30f) == 0xfe);
+  EXPECT(encode_e4m3(0.0f) == 0x00 && encode_e4m3(-0.0f) == 0x80);
+  EXPECT(decode_e4m3(0x38) == 1.0f && decode_e4m3(0x01) == 0.001953125f);
+  EXPECT(encode_f16(65504.0f) == 0x7bff && encode_f16(65520.0f) == 0x7c00 && encode_f16(5.9604645e-8f) == 0x0001);
+  EXPECT(encode_bf16(1.0f) == 0x3f80 && decode_bf16(0x4049) == 3.140625f);
+  EXPECT(reference_f16_bits(0, 0) == 0x0000);  // mix = 7 -> table entry 7
+}
+
+}  // namespace
+
+int main() {
+  test_json_report();
+  test_human_report_and_status();
+  test_bandwidth_and_csv();
+  test_align_up_and_json_writer();
+  test_topology_validation();
+  test_status_text();
+  test_codec_spot_checks();
+  if (g_failures == 0) {
+    std::printf("all native tests passed\n");
+    return 0;
+  }
+  std::printf("%d native test failure(s)\n", g_failures);
+  return 1;
+}

@@ -1,0 +1,78 @@
+"""Tensor-parallel layers built on the fused GEMM + all-reduce.
+
+`RowParallelLinearFP8` is the row-parallel half of a Megatron-style MLP: the input features
+(K) are split over the ranks, every rank multiplies its slice, and the partial products are
+summed so that every rank holds the full output. Weights and activations are FP8 E4M3 with
+float block scales (1 x 128 for activations, 128 x 128 for weights); the output is BF16 in
+symmetric memory. The all-reduce happens inside the GEMM kernel, tile by tile, through the
+NVSwitch. The reference project stops at the collective itself; this layer is the consumer
+that its in-switch reduction is built for (the down-projection of a Llama-70B FFN split eight
+ways is the benchmarked case).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.gemm_allreduce import BLOCK, GemmAllReduce, dequantize_blockwise, quantize_blockwise
+from ..parallel.symmetric import Communicator
+
+
+class RowParallelLinearFP8(torch.nn.Module):
+    """y = sum over ranks of x_r @ W_r^T, with x_r [tokens, in_features / world] on rank r."""
+
+    def __init__(self, comm: Communicator, in_features: int, out_features: int, max_tokens: int,
+                 weight: torch.Tensor | None = None, seed: int = 0):
+        super().__init__()
+        if in_features % (comm.world * BLOCK) or out_features % BLOCK or max_tokens % BLOCK:
+            raise ValueError("in_features / world, out_features and max_tokens must be multiples of 128")
+        self.comm = comm
+        self.in_features = in_features
+        self.out_features = out_features
+        self.k_local = in_features // comm.world
+        self.max_tokens = max_tokens
+        if weight is None:
+            g = torch.Generator(device="cuda").manual_seed(seed)  # same full weight on every rank, then sliced
+            weight = torch.randn(out_features, in_features, device="cuda", generator=g) / in_features ** 0.5
+        local = weight[:, comm.rank * self.k_local:(comm.rank + 1) * self.k_local].contiguous()
+        q, s = quantize_blockwise(local, BLOCK)
+        self.register_buffer("weight_fp8", q)
+        self.register_buffer("weight_scale", s)
+        self._ops: dict[int, GemmAllReduce] = {}
+
+    def _op(self, tokens: int) -> GemmAllReduce:
+        if tokens not in self._ops:
+            self._ops[tokens] = GemmAllReduce(self.comm, tokens, self.out_features)
+        return self._ops[tokens]
+
+    def forward_quantized(self, x_fp8: torch.Tensor, x_scale: torch.Tensor) -> torch.Tensor:
+        return self._op(x_fp8.shape[0])(x_fp8, x_scale, self.weight_fp8, self.weight_scale)
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        """x_local: [tokens, in_features / world] in any float dtype; quantised per 1 x 128 block."""
+        tokens = x_local.shape[0]
+        if tokens % BLOCK or tokens > self.max_tokens:
+            raise ValueError("the token count must be a multiple of 128 and at most max_tokens")
+        q, s = quantize_blockwise(x_local, 1)
+        return self.forward_quantized(q, s)
+
+    def reference(self, x_local: torch.Tensor) -> torch.Tensor:
+        """This rank's partial product in plain float32 (sum it over the ranks to compare)."""
+        q, s = quantize_blockwise(x_local, 1)
+        return dequantize_blockwise(q, s, 1) @ dequantize_blockwise(self.weight_fp8, self.weight_scale, BLOCK).t()
+
+    def free(self) -> None:
+        for op in self._ops.values():
+            op.free()
+        self._ops.clear()
+
+
+class TensorParallelFFNDown(torch.nn.Module):
+    """Second half of a gated FFN under tensor parallelism: act(gate) * up is computed locally on
+    this rank's slice of the hidden dimension and fed to the row-parallel down-projection."""
+
+    def __init__(self, comm: Communicator, hidden: int, intermediate: int, max_tokens: int, seed: int = 0):
+        super().__init__()
+        self.down = RowParallelLinearFP8(comm, intermediate, hidden, max_tokens, seed=seed)
+
+    def forward(self, gate_local: torch.Tensor, up_local: torch.Tensor) -> torch.Tensor:
+        return self.down(torch.nn.functional.silu(gate_local.float()) * up_local.float())

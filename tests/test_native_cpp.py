@@ -1,0 +1,11 @@
+"""Runs the C++ unit-test executable that the in-tree build produces (host code, no GPU)."""
+import subprocess
+
+from mnnvl_sharp_b200 import _build
+
+
+def test_native_cpp_suite():
+    paths = _build.build_native()
+    proc = subprocess.run([str(paths["tests"])], capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "all native tests passed" in proc.stdout
