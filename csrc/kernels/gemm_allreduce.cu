@@ -12,6 +12,7 @@
 //               cannot be left to the tensor core); after the last K block the BF16 row is stored
 //               to this rank's copy of the symmetric output and the tile's arrival is counted
 //               at the tile's owner with one release-add over NVLink
+//   warp 14     (several ranks) waits for the epilogue's tile stores and publishes the tile
 //   warps 10-13 reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
 //               wait until every rank has published the tile, then multimem.ld_reduce (float32
 //               accumulation in the switch) + multimem.st the tile in place, so that the sum
@@ -41,11 +42,13 @@ constexpr int kStageBytesA = BM * BK;  // FP8: one byte per element
 constexpr int kStageBytesB = BN * BK;
 constexpr int kUmmaK = 32;             // K extent of one kind::f8f6f4 instruction
 constexpr int kTmemCols = 256;         // two float32 accumulators of 128 columns
-constexpr int kThreads = 448;          // 14 warps
+constexpr int kThreads = 480;          // 15 warps
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter, each taking half of the columns
 constexpr int kEpilogueCols = BN / 2;
 constexpr int kReducerWarp0 = kEpilogueWarp0 + kEpilogueWarps;
+constexpr int kReducerWarps = 4;
+constexpr int kSignalWarp = kReducerWarp0 + kReducerWarps;  // publishes finished tiles so that no epilogue thread waits for its stores to drain
 constexpr int kSmemBytes = kStages * (kStageBytesA + kStageBytesB) + 1024;  // + alignment slack
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -271,7 +274,15 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int row_in_tile = quarter * 32 + lane;
     const int etid = (warp - kEpilogueWarp0) * 32 + lane;
     uint32_t it = 0;
-    for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
+    // Every tile ends with exactly one arrival per thread on the publisher's barrier, also after a
+    // timeout, so that the publisher warp (which can only wait on that barrier) always gets out.
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      if (s_abort) {
+        if constexpr (MULTI) {
+          asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
+        }
+        continue;
+      }
       const int mt = t / tiles_n;
       const int nt = t % tiles_n;
       const int row = mt * BM + row_in_tile;
@@ -317,7 +328,10 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       }
       if (!ok) {
-        break;
+        if constexpr (MULTI) {
+          asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
+        }
+        continue;
       }
       // BF16 half-row of this tile into this rank's copy of the output (the partial product when
       // several ranks take part, the final result otherwise)
@@ -333,9 +347,18 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         dst[q] = v;
       }
       if constexpr (MULTI) {
-        // the whole tile is stored, then one release-add tells the owner of the tile
-        named_barrier(1, kEpilogueWarps * 32);
-        if (etid == 0) {
+        // hand the stored tile to the signal warp without waiting (arrive, not sync)
+        asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
+      }
+      (void)etid;
+    }
+  } else if (warp == kSignalWarp) {
+    // ------------------------------------------------------------------ tile publisher
+    if constexpr (MULTI) {
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        // completes when all epilogue threads have stored their part of tile t (they only arrive)
+        named_barrier(1, kEpilogueWarps * 32 + 32);
+        if (lane == 0 && !s_abort) {
           const int owner = t % comm.world;
           uint32_t* flag = reinterpret_cast<uint32_t*>(p.ws_peers.ptr[owner] + kGemmWsFlagOffset) + t;
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
@@ -375,23 +398,19 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const int nt = static_cast<int>(t) % tiles_n;
           // 128 rows x 256 bytes: 16 vectors per row; thread -> (row, vector) with rows interleaved
           __nv_bfloat16* tile_mc = p.out_mc + static_cast<size_t>(mt) * BM * p.n + static_cast<size_t>(nt) * BN;
-#pragma unroll 1
-          for (int base = 0; base < BM * 16; base += 128 * 4) {
-            dev::Vec4 v[4];
+          // the whole tile (2048 vectors, 16 per thread) is requested before the first store, so one
+          // switch round trip covers the tile instead of several
+          constexpr int kVecPerThread = BM * 16 / 128;
+          dev::Vec4 v[kVecPerThread];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int idx = base + u * 128 + rtid;
-              const int r = idx >> 4;
-              const int c = idx & 15;
-              v[u] = dev::ld_reduce_v4<dev::kReduceBF16AccF32>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(r) * p.n) + c);
-            }
+          for (int u = 0; u < kVecPerThread; ++u) {
+            const int idx = u * 128 + rtid;
+            v[u] = dev::ld_reduce_v4<dev::kReduceBF16AccF32>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(idx >> 4) * p.n) + (idx & 15));
+          }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int idx = base + u * 128 + rtid;
-              const int r = idx >> 4;
-              const int c = idx & 15;
-              dev::st_all_v4<false>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(r) * p.n) + c, v[u]);
-            }
+          for (int u = 0; u < kVecPerThread; ++u) {
+            const int idx = u * 128 + rtid;
+            dev::st_all_v4<false>(reinterpret_cast<uint4*>(tile_mc + static_cast<size_t>(idx >> 4) * p.n) + (idx & 15), v[u]);
           }
         }
         dev::fence_proxy_alias();
@@ -459,7 +478,9 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
   // The grid is always one CTA per SM so that the reducer CTAs (which wait for their peers) are
   // resident and so that the same barrier slots are used by every launch.
   const int grid = sms;
-  p.reducer_ctas = std::min(grid, a.reducer_ctas > 0 ? a.reducer_ctas : 32);
+  // 32 reducer CTAs keep up with the tile rate at any world size (one tile per switch round trip
+  // each); more only add queued requests, and every CTA reducing was measured to stall at 2 ranks.
+  p.reducer_ctas = std::min(std::min(grid, 64), a.reducer_ctas > 0 ? a.reducer_ctas : 32);
 
   const CUtensorMap map_a = make_tile_map(api, a.a, a.m, a.k);
   const CUtensorMap map_w = make_tile_map(api, a.w, a.n, a.k);
