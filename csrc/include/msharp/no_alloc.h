@@ -1,0 +1,47 @@
+// Replica hash without any allocation. This entry point has no counterpart in the reference
+// project.
+//
+// Who needs it: code that must not allocate device memory while it runs. Two cases this library
+// meets in practice: (1) a process that has handed every byte of the GPU to its own pool (an
+// inference server, a framework with a hard memory cap): there a cudaMalloc made on the side
+// either fails or takes memory that the pool believes it owns; (2) a checker that runs beside a
+// job in flight (a monitor that compares replica hashes between training steps): an allocation
+// can make the whole device wait, which such a checker must never cause. Both can still pass
+// pointers to memory they already own, which is all this function asks for.
+//
+// What it does: the same order-independent 64-bit hash as msharp_hash_device (XOR over
+// mix64((word << 32) ^ word_index) of all 32-bit words), written to `out_hash_device`. Where the
+// regular kernel accumulates into memory that its caller allocates and clears, this variant
+// keeps its partial results and its arrival counter in a fixed array that is part of the library
+// image (`static __device__`, 8448 bytes; every GPU that loads the library carries it until the
+// process exits).
+//
+// Limits and rules:
+//   * at most kNoAllocHashMaxBytes (4 GiB) per call: one partial-result slot per 4 MiB of input,
+//     1024 slots; larger inputs are refused with an error, nothing is launched;
+//   * `data` 16-byte aligned, `bytes` a multiple of 4, `out_hash_device` 8-byte aligned device memory;
+//   * the first call on each device looks up the device address of the built-in array
+//     (cudaGetSymbolAddress, with that device current). Make that first call before any stream
+//     capture begins;
+//   * all calls on one device share the array. The function clears what has to start at zero
+//     itself, but two calls that overlap on the GPU (different streams, no ordering between
+//     them) race on it and give wrong hashes: order them;
+//   * no cudaMalloc, cudaFree or allocating library call is made, on any path.
+// Returns 0, or non-zero with the text available from msharp_no_alloc_last_error() (per thread).
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSHARP_NO_ALLOC_HASH_MAX_BYTES (4ull << 30)
+
+int msharp_hash_no_alloc(uint64_t data, size_t bytes, uint64_t out_hash_device, uint64_t stream);
+const char* msharp_no_alloc_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

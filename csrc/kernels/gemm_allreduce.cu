@@ -4,7 +4,7 @@
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and W tiles (128 x 128 bytes
 //               each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
-//               two TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
+//               four TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
 //   warps 2-9   promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
 //               tcgen05.ld of the 128-deep partial product, multiply by
 //               a_scale[row, kblock] * w_scale[ntile, kblock], accumulate in float32 registers
@@ -41,7 +41,8 @@ constexpr int kStages = 6;
 constexpr int kStageBytesA = BM * BK;  // FP8: one byte per element
 constexpr int kStageBytesB = BN * BK;
 constexpr int kUmmaK = 32;             // K extent of one kind::f8f6f4 instruction
-constexpr int kTmemCols = 256;         // two float32 accumulators of 128 columns
+constexpr int kAccBuffers = 4;         // float32 accumulators of 128 columns each in flight between MMA and promotion
+constexpr int kTmemCols = kAccBuffers * BN;  // 512: all of the SM's tensor memory (one CTA per SM)
 constexpr int kThreads = 480;          // 15 warps
 constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter, each taking half of the columns
@@ -182,8 +183,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
   __shared__ __align__(8) uint64_t bar_full[kStages];
   __shared__ __align__(8) uint64_t bar_empty[kStages];
-  __shared__ __align__(8) uint64_t bar_acc_full[2];
-  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_acc_full[kAccBuffers];
+  __shared__ __align__(8) uint64_t bar_acc_empty[kAccBuffers];
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_barrier_ok;
@@ -199,7 +200,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       mbar_init(&bar_full[s], 1);
       mbar_init(&bar_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAccBuffers; ++b) {
       mbar_init(&bar_acc_full[b], 1);
       mbar_init(&bar_acc_empty[b], kEpilogueWarps);  // one arrival per epilogue warp
     }
@@ -244,8 +245,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
-          const int buf = it & 1;
-          const uint32_t acc_phase = (it >> 1) & 1u;
+          const int buf = it % kAccBuffers;
+          const uint32_t acc_phase = (it / kAccBuffers) & 1u;
           if (!mbar_wait(&bar_acc_empty[buf], acc_phase ^ 1u, comm.timeout_ns) ||
               !mbar_wait(&bar_full[s], phase, comm.timeout_ns)) {
             dev::report(comm, kStatusCopyTimeout, 0x200u + s);
@@ -297,8 +298,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       // the scale of the next K block is fetched while the current one is being accumulated
       float next_scale = __ldg(a_scale_row) * __ldg(w_scale_row);
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1u;
+        const int buf = it % kAccBuffers;
+        const uint32_t acc_phase = (it / kAccBuffers) & 1u;
         const float scale = next_scale;
         if (kb + 1 < k_blocks) {
           next_scale = __ldg(a_scale_row + kb + 1) * __ldg(w_scale_row + kb + 1);
