@@ -707,7 +707,8 @@ int msharp_gemm_allreduce(void* comm, void* out_symm, uint64_t a, uint64_t a_sca
     args.n = n;
     args.k = k;
     args.out_local = reinterpret_cast<void*>(out.output_ptr(out.rank()));
-    args.reducer_ctas = reducer_ctas;
+    args.reducer_ctas = reducer_ctas & 0xffff;
+    args.tile_n = (reducer_ctas >> 16) & 0xffff;  // optional tile width (128 / 256) in the upper half
     uint64_t peers[msharp::kMaxWorld] = {0};
     if (out.world() > 1) {
       if (out.mc_base == 0) {

@@ -99,7 +99,8 @@ int msharp_bulk_multimem_compiled(void);
 int msharp_gemm_workspace_init(void* comm);
 // out_symm: symmetric buffer holding the BF16 [m, n] result (payload >= m * n * 2 bytes, with a
 // multicast alias when world > 1). a: [m, k] e4m3, a_scales: float [m, k/128], w: [n, k] e4m3,
-// w_scales: float [n/128, k/128]; all device pointers. reducer_ctas: 0 = default.
+// w_scales: float [n/128, k/128]; all device pointers. reducer_ctas: 0 = default; its upper 16 bits
+// may carry an explicit tile width (128 or 256), 0 = default (128).
 int msharp_gemm_allreduce(void* comm, void* out_symm, uint64_t a, uint64_t a_scales, uint64_t w, uint64_t w_scales,
                           int m, int n, int k, int reducer_ctas, uint64_t stream);
 

@@ -45,6 +45,7 @@ struct GemmAllReduceArgs {
   unsigned char* ws_local = nullptr;
   const uint64_t* ws_peers = nullptr;  // host array [world]: workspace address of every rank as mapped here
   int reducer_ctas = 0;  // 0 = default: how many CTAs also run reduction warps
+  int tile_n = 0;        // 0 = default (128); or 128 / 256 explicitly (256 needs N % 256 == 0)
 };
 
 // Enqueues the fused kernel. M and N must be multiples of 128, K a multiple of 128; pointers

@@ -46,6 +46,25 @@ def test_gemm_matches_fp32_reference(comm, m, n, k):
     op.free()
 
 
+def test_wide_tile_variant_gives_the_same_result(comm):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    m, n, k = 384, 512, 768
+    torch.manual_seed(9)
+    a, sa = ops.quantize_blockwise(torch.randn(m, k, device="cuda") / k ** 0.5, 1)
+    w, sw = ops.quantize_blockwise(torch.randn(n, k, device="cuda") / k ** 0.5, 128)
+    sw = (sw * (1.0 + torch.rand_like(sw))).contiguous()
+    op = ops.GemmAllReduce(comm, m, n)
+    narrow = op(a, sa, w, sw, reducer_ctas=128 << 16).clone()
+    wide = op(a, sa, w, sw, reducer_ctas=256 << 16).clone()
+    torch.cuda.synchronize()
+    comm.raise_if_failed("gemm")
+    assert torch.equal(narrow, wide)
+    op.free()
+
+
 def test_gemm_rejects_bad_shapes(comm):
     import torch
 
