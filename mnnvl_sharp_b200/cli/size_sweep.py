@@ -5,7 +5,7 @@ also appended to --csv as they are produced, and points already present there ar
 interrupted sweep resumes where it stopped.
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m mnnvl_sharp_b200.cli.size_sweep --nccl --csv gpurun_out/size_sweep.csv
+        -m mnnvl_sharp_b200.cli.size_sweep --nccl --csv size_sweep.csv
 """
 from __future__ import annotations
 
