@@ -65,8 +65,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 // Bounded wait for the phase with the given parity. Returns false when the deadline passed.
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity, unsigned long long timeout_ns);
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns) {
-  const uint32_t addr = smem_addr(bar);
+  return mbar_wait_addr(smem_addr(bar), parity, timeout_ns);
+}
+
+__device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity, unsigned long long timeout_ns) {
   unsigned long long start = 0;
   for (uint32_t spins = 0;; ++spins) {
     uint32_t done;
@@ -115,6 +119,10 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit TMEM words: thread i of the warp gets lane (base + i), 32 columns.
 // Issue only (no wait): the caller overlaps several loads and waits once.
 __device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t* r) {
@@ -146,6 +154,16 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile, uint32_t b
 // Instruction descriptor: float32 accumulator, E4M3 x E4M3, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) {
   return (1u << 4) | (0u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// One lane of a converged warp. The warp keeps executing the surrounding loop as a whole, so its
+// loop variables stay warp-uniform (the tensor-core and TMA instructions take their operands
+// from uniform registers; values computed by a single diverged lane would have to be moved there
+// one by one before every instruction, which was measured to cost ~100 cycles per MMA).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+  return elected != 0;
 }
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
@@ -224,50 +242,74 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (warp < kEpilogueWarp0) {
     // ================================================================== warp group 0: TMA, MMA, publisher
     if (warp == kTmaWarp) {
-      if (lane == 0) {
-        uint32_t it = 0;
-        for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
-          const int m0 = (t / tiles_n) * BM;
-          const int n0 = (t % tiles_n) * TN;
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            const int s = it % kStagesT;
-            const uint32_t phase = (it / kStagesT) & 1u;
-            if (!mbar_wait(&bar_empty[s], phase ^ 1u, comm.timeout_ns)) {
+      uint32_t s = 0, phase = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < total_tiles && alive && !s_abort; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * BM;
+        const int n0 = (t % tiles_n) * TN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&bar_empty[s], phase ^ 1u, comm.timeout_ns)) {
+            if (lane == 0) {
               dev::report(comm, kStatusCopyTimeout, 0x100u + s);
               s_abort = 1;
-              break;
             }
+            alive = false;
+            break;
+          }
+          if (elect_one()) {
             mbar_expect_tx(&bar_full[s], kStageBytesA + kStageBytesBT);
             tma_load_2d(smem_a + s * kStageBytesA, &map_a, kb * BK, m0, &bar_full[s]);
             tma_load_2d(smem_b + s * kStageBytesBT, &map_w, kb * BK, n0, &bar_full[s]);
           }
+          __syncwarp();
+          if (++s == kStagesT) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
       }
     } else if (warp == kMmaWarp) {
-      if (lane == 0) {
-        constexpr uint32_t idesc = umma_idesc_e4m3(BM, TN);
-        uint32_t it = 0;
-        for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x) {
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            const int s = it % kStagesT;
-            const uint32_t phase = (it / kStagesT) & 1u;
-            const int buf = it % kAccBuffersT;
-            const uint32_t acc_phase = (it / kAccBuffersT) & 1u;
-            if (!mbar_wait(&bar_acc_empty[buf], acc_phase ^ 1u, comm.timeout_ns) ||
-                !mbar_wait(&bar_full[s], phase, comm.timeout_ns)) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(BM, TN);
+      const uint64_t desc_a0 = umma_desc_sw128(smem_a, 0);
+      const uint64_t desc_b0 = umma_desc_sw128(smem_b, 0);
+      const uint32_t full0 = smem_addr(&bar_full[0]);
+      const uint32_t empty0 = smem_addr(&bar_empty[0]);
+      const uint32_t acc_full0 = smem_addr(&bar_acc_full[0]);
+      const uint32_t acc_empty0 = smem_addr(&bar_acc_empty[0]);
+      uint32_t s = 0, phase = 0, buf = 0, acc_phase = 0;
+      bool alive = true;
+      for (int t = blockIdx.x; t < total_tiles && alive && !s_abort; t += gridDim.x) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_addr(acc_empty0 + buf * 8, acc_phase ^ 1u, comm.timeout_ns) ||
+              !mbar_wait_addr(full0 + s * 8, phase, comm.timeout_ns)) {
+            if (lane == 0) {
               dev::report(comm, kStatusCopyTimeout, 0x200u + s);
               s_abort = 1;
-              break;
             }
-            tc_fence_after();
-            const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * TN);
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t acc = tmem_base + buf * TN;
+          const uint64_t da = desc_a0 + static_cast<uint64_t>(s * (kStageBytesA >> 4));
+          const uint64_t db = desc_b0 + static_cast<uint64_t>(s * (kStageBytesBT >> 4));
+          if (elect_one()) {
 #pragma unroll
             for (int k = 0; k < BK / kUmmaK; ++k) {
-              umma_f8(acc, umma_desc_sw128(smem_a + s * kStageBytesA, k * kUmmaK),
-                      umma_desc_sw128(smem_b + s * kStageBytesBT, k * kUmmaK), idesc, k > 0 ? 1u : 0u);
+              // the next 32-byte K slice is 2 units of 16 bytes further in the start-address field
+              umma_f8(acc, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
             }
-            umma_commit(&bar_empty[s]);       // the stage may be refilled once these MMAs have read it
-            umma_commit(&bar_acc_full[buf]);  // and the 128-deep partial product is ready for promotion
+            umma_commit_addr(empty0 + s * 8);        // the stage may be refilled once these MMAs have read it
+            umma_commit_addr(acc_full0 + buf * 8);   // and the 128-deep partial product is ready for promotion
+          }
+          __syncwarp();
+          if (++s == kStagesT) {
+            s = 0;
+            phase ^= 1u;
+          }
+          if (++buf == kAccBuffersT) {
+            buf = 0;
+            acc_phase ^= 1u;
           }
         }
       }
@@ -311,14 +353,30 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         acc[j] = 0.0f;
       }
       bool ok = true;
-      // the scale of the next K block is fetched while the current one is being accumulated
-      float next_scale = __ldg(a_scale_row) * __ldg(w_scale_row);
+      // Scales are fetched kScaleAhead K blocks before their use and kept as raw values: a warp
+      // runs in order, so multiplying them right after the load would park the whole warp for one
+      // cache / memory latency in every K block.
+      constexpr int kScaleAhead = 4;
+      float a_raw[kScaleAhead], w_raw[kScaleAhead];
+#pragma unroll
+      for (int j = 0; j < kScaleAhead; ++j) {
+        const int kb = j < k_blocks ? j : k_blocks - 1;
+        a_raw[j] = __ldg(a_scale_row + kb);
+        w_raw[j] = __ldg(w_scale_row + kb);
+      }
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int buf = it % kAccBuffersT;
         const uint32_t acc_phase = (it / kAccBuffersT) & 1u;
-        const float scale = next_scale;
-        if (kb + 1 < k_blocks) {
-          next_scale = __ldg(a_scale_row + kb + 1) * __ldg(w_scale_row + kb + 1);
+        const float scale = a_raw[0] * w_raw[0];
+#pragma unroll
+        for (int j = 0; j + 1 < kScaleAhead; ++j) {
+          a_raw[j] = a_raw[j + 1];
+          w_raw[j] = w_raw[j + 1];
+        }
+        {
+          const int ahead = kb + kScaleAhead < k_blocks ? kb + kScaleAhead : k_blocks - 1;
+          a_raw[kScaleAhead - 1] = __ldg(a_scale_row + ahead);
+          w_raw[kScaleAhead - 1] = __ldg(w_scale_row + ahead);
         }
         if (!mbar_wait(&bar_acc_full[buf], acc_phase, comm.timeout_ns)) {
           dev::report(comm, kStatusCopyTimeout, 0x300u + buf);
