@@ -14,9 +14,11 @@
 #include "msharp/runner.h"
 
 #include <cuda_runtime_api.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <chrono>
 #include <cstdlib>
+#include <fstream>
 #include <iostream>
 #include <memory>
 #include <sstream>
@@ -35,6 +37,12 @@ namespace msharp {
 namespace {
 
 using Clock = std::chrono::steady_clock;
+
+// Named range on the profiler timeline (no cost when no tool is attached).
+struct TraceRange {
+  explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+  ~TraceRange() { nvtxRangePop(); }
+};
 
 double ms_since(Clock::time_point t0) { return std::chrono::duration<double, std::milli>(Clock::now() - t0).count(); }
 
@@ -79,6 +87,7 @@ void agree_on_device_status(RankRun& run, const char* what) {
 }
 
 void canary_smoke_test(RankRun& run) {
+  const TraceRange trace("canary_smoke_test");
   const int world = run.rank.world_size;
   launch_canary_write(static_cast<uint32_t*>(run.input_ptr()), run.rank.world_rank, run.stream);
   launch_alias_fence(run.stream);
@@ -150,6 +159,7 @@ void launch_collective(RankRun& run) {
 }
 
 void run_iteration(RankRun& run, bool measure, double* device_ms, double* wall_ms) {
+  const TraceRange trace(measure ? "allreduce_iteration_measured" : "allreduce_iteration_warmup");
   initialize_buffers(run);
   run.comm.barrier();  // every rank's input is in place
   const auto t0 = Clock::now();
@@ -233,7 +243,9 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   std::string failure;
   try {
     const auto c0 = Clock::now();
+    nvtxRangePushA("control_block_init");
     run.ctx = CommContext::create(api, comm, base, cfg.wait_timeout_ms);
+    nvtxRangePop();
     report.control_init_ms = ms_since(c0);
 
     SymmOptions data = base;
@@ -241,7 +253,9 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
     data.layout = cfg.sharp_backend == Backend::kTmaAsync ? RegionLayout::kInputOutput : RegionLayout::kSingle;
     // the fan-out form of the bulk backend and the software path write through unicast mappings
     data.want_multicast = cfg.sharp_backend != Backend::kTmaAsync || bulk_multimem_compiled();
+    nvtxRangePushA("symmetric_memory_init");
     run.mem = SymmetricMemory::create(api, comm, data);
+    nvtxRangePop();
     if ((cfg.sharp_backend == Backend::kLegacy || cfg.sharp_backend == Backend::kPull) && world > 1 &&
         run.mem->mc_base == 0) {
       throw std::runtime_error("the multicast alias could not be created; this backend needs it");
@@ -384,6 +398,13 @@ int run_cpu_only(const Config& cfg, std::ostream& out) {
   reduce_semantic(dtype, spec, 0, elements, semantic.data());
   const double semantic_ms = ms_since(t1);
   const PrecisionMetrics m = compare(dtype, spec, expected.data(), std::min(elements, cfg.reference_check_bytes / dtype_size(dtype)));
+  if (!cfg.dump_expected.empty()) {
+    std::ofstream file(cfg.dump_expected, std::ios::binary);
+    file.write(reinterpret_cast<const char*>(expected.data()), static_cast<std::streamsize>(expected.size()));
+    if (!file) {
+      throw std::runtime_error("cannot write " + cfg.dump_expected);
+    }
+  }
   const uint64_t hash_f32 = hash_words(reinterpret_cast<const uint32_t*>(expected.data()), cfg.bytes / 4);
   const uint64_t hash_sem = hash_words(reinterpret_cast<const uint32_t*>(semantic.data()), cfg.bytes / 4);
 

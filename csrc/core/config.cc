@@ -175,7 +175,7 @@ std::string usage(const char* argv0) {
      << "extensions: [--sharp-backend pull|sw_f32] [--types bf16] [--pattern reference|seeded|tagged]"
      << " [--seed N] [--acc auto|f16|f32] [--handle-type auto|posix_fd|fabric] [--grid N] [--block N]"
      << " [--unroll N] [--wait-timeout-ms 2000] [--no-pin] [--session NAME] [--reference-geometry]"
-     << " [--cpu-only]\n";
+     << " [--cpu-only [--dump-expected FILE]]\n";
   return os.str();
 }
 
@@ -235,6 +235,7 @@ Config parse_config(const std::vector<std::string>& args) {
       {"--unroll", [&](const std::string& f) { cfg.unroll = parse_int_strict(value_of(f), f); }},
       {"--wait-timeout-ms", [&](const std::string& f) { cfg.wait_timeout_ms = parse_int_strict(value_of(f), f); }},
       {"--session", [&](const std::string& f) { cfg.session = value_of(f); }},
+      {"--dump-expected", [&](const std::string& f) { cfg.dump_expected = value_of(f); }},
   };
   const std::map<std::string, bool Config::*> switches = {
       {"--init-only", &Config::init_only},
@@ -308,6 +309,9 @@ Config parse_config(const std::vector<std::string>& args) {
   }
   if (cfg.block != 0 && (cfg.block % 32 != 0 || cfg.block > 1024)) {
     throw std::invalid_argument("--block must be a multiple of 32 and at most 1024");
+  }
+  if (!cfg.dump_expected.empty() && !cfg.cpu_only) {
+    throw std::invalid_argument("--dump-expected needs --cpu-only");
   }
   if (cfg.wait_timeout_ms <= 0) {
     throw std::invalid_argument("--wait-timeout-ms must be >= 1");

@@ -53,6 +53,7 @@ struct Config {
   std::string session;         // bootstrap session name (default derived from the launcher pid)
   bool reference_geometry = false;  // run the rank-0-only scalar launch shape of the reference
   bool cpu_only = false;       // oracle only: no GPU, synthetic ranks reduced on the host
+  std::string dump_expected;   // with --cpu-only: file that receives the expected result bytes (cast of the float32 sum)
 };
 
 const char* to_string(Backend b);

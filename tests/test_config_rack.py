@@ -219,6 +219,34 @@ def test_cpu_only_oracle_run(tmp_path):
     assert again["expected_f32_cast_hash"] == out["expected_f32_cast_hash"]
 
 
+def test_cpu_only_binary_dumps_the_bitwise_expected_result(tmp_path):
+    import json
+    import subprocess
+
+    import numpy as np
+
+    from mnnvl_sharp_b200 import _build
+    from mnnvl_sharp_b200.utils import numerics as nm
+
+    exe = _build.build_native()["exe"]
+    path = tmp_path / "rack.yaml"
+    path.write_text(RACK_2X4)
+    out = tmp_path / "expected.bin"
+    for types, backend, dtype in (("e4m3", "legacy", "e4m3"), ("f16", "tma_async", "f16")):
+        proc = subprocess.run([str(exe), "--rack-config", str(path), "--rank-count", "8", "--cpu-only", "--pattern", "seeded",
+                               "--sharp-backend", backend, "--types", types, "--bytes", "65536",
+                               "--reference-check-bytes", "65536", "--dump-expected", str(out)],
+                              capture_output=True, text=True, timeout=120)
+        assert proc.returncode == 0, proc.stderr
+        summary = json.loads(proc.stdout.strip().splitlines()[-1])
+        assert summary["datatype"] == dtype and summary["selected_rank_count"] == 8
+        got = np.fromfile(out, dtype=nm.storage_dtype(dtype))
+        assert np.array_equal(got, nm.reduce_f32_cast(dtype, "seeded", 8, got.size))
+        assert int(summary["expected_f32_cast_hash"], 16) == nm.hash_words(got)
+    with pytest.raises(NativeError, match="--dump-expected needs --cpu-only"):
+        cli("--dump-expected", "x.bin")
+
+
 def test_csv_header():
     assert rack.CSV_HEADER == ("rank_count,repeat,sharp_backend,peer_init_ms,peer_init_min_ms,peer_init_median_ms,"
                                "peer_init_p95_ms,peer_init_max_ms")
