@@ -3,7 +3,7 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and W tiles (128 x 128 bytes
 //               each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
-//   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
+//   warps 1, 3  MMA issuers (alternate K blocks): tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
 //               four TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
 //   warps 2-9   promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
 //               tcgen05.ld of the 128-deep partial product, multiply by
@@ -40,9 +40,10 @@ constexpr int BK = kGemmTileK;
 constexpr int kStageBytesA = BM * BK;  // FP8: one byte per element
 constexpr int kUmmaK = 32;             // K extent of one kind::f8f6f4 instruction
 constexpr int kTmemCols = 512;         // all of the SM's tensor memory (one CTA per SM): 4 x 128 or 2 x 256 columns
-constexpr int kThreads = 512;          // 16 warps: 4 control (TMA, MMA, publisher, spare), 8 promotion, 4 reducers
+constexpr int kThreads = 512;          // 16 warps: 4 control (TMA, two MMA issuers, publisher), 8 promotion, 4 reducers
 constexpr int kTmaWarp = 0;
 constexpr int kMmaWarp = 1;
+constexpr int kMmaWarp2 = 3;
 constexpr int kSignalWarp = 2;         // publishes finished tiles so that no promotion thread waits for its stores to drain
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kEpilogueWarps = 8;      // two per TMEM lane quarter, each taking half of the columns
@@ -265,48 +266,46 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           }
         }
       }
-    } else if (warp == kMmaWarp) {
+    } else if (warp == kMmaWarp || warp == kMmaWarp2) {
+      // Two issuer warps take alternate K blocks. One issuer spends ~700 cycles per K block on its
+      // own chain of waits, fence, four MMAs and a commit (measured), against 256 cycles of tensor
+      // work; K blocks are independent of each other (each goes to its own accumulator and is
+      // summed later in registers), so two chains run side by side.
       constexpr uint32_t idesc = umma_idesc_e4m3(BM, TN);
+      constexpr uint32_t kIssuers = 2;
       const uint64_t desc_a0 = umma_desc_sw128(smem_a, 0);
       const uint64_t desc_b0 = umma_desc_sw128(smem_b, 0);
       const uint32_t full0 = smem_addr(&bar_full[0]);
       const uint32_t acc_full0 = smem_addr(&bar_acc_full[0]);
       const uint32_t acc_empty0 = smem_addr(&bar_acc_empty[0]);
-      uint32_t s = 0, phase = 0, buf = 0, acc_phase = 0;
-      bool alive = true;
-      for (int t = blockIdx.x; t < total_tiles && alive && !s_abort; t += gridDim.x) {
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_addr(acc_empty0 + buf * 8, acc_phase ^ 1u, comm.timeout_ns) ||
-              !mbar_wait_addr(full0 + s * 8, phase, comm.timeout_ns)) {
-            if (lane == 0) {
-              dev::report(comm, kStatusCopyTimeout, 0x200u + s);
-              s_abort = 1;
-            }
-            alive = false;
-            break;
+      const uint32_t my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                                    ? static_cast<uint32_t>((total_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1)
+                                    : 0u;
+      const uint32_t total_its = my_tiles * static_cast<uint32_t>(k_blocks);
+      for (uint32_t it = (warp == kMmaWarp ? 0u : 1u); it < total_its && !s_abort; it += kIssuers) {
+        const uint32_t s = it % kStagesT;              // stage and accumulator rotate together
+        const uint32_t phase = (it / kStagesT) & 1u;
+        if (!mbar_wait_addr(acc_empty0 + s * 8, phase ^ 1u, comm.timeout_ns) ||
+            !mbar_wait_addr(full0 + s * 8, phase, comm.timeout_ns)) {
+          if (lane == 0) {
+            dev::report(comm, kStatusCopyTimeout, 0x200u + s);
+            s_abort = 1;
           }
-          tc_fence_after();
-          const uint32_t acc = tmem_base + buf * TN;
-          const uint64_t da = desc_a0 + static_cast<uint64_t>(s * (kStageBytesA >> 4));
-          const uint64_t db = desc_b0 + static_cast<uint64_t>(s * (kStageBytesBT >> 4));
-          if (elect_one()) {
-#pragma unroll
-            for (int k = 0; k < BK / kUmmaK; ++k) {
-              // the next 32-byte K slice is 2 units of 16 bytes further in the start-address field
-              umma_f8(acc, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
-            }
-            umma_commit_addr(acc_full0 + buf * 8);   // partial product ready for promotion; stage may be refilled
-          }
-          __syncwarp();
-          if (++s == kStagesT) {
-            s = 0;
-            phase ^= 1u;
-          }
-          if (++buf == kAccBuffersT) {
-            buf = 0;
-            acc_phase ^= 1u;
-          }
+          break;
         }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + s * TN;
+        const uint64_t da = desc_a0 + static_cast<uint64_t>(s * (kStageBytesA >> 4));
+        const uint64_t db = desc_b0 + static_cast<uint64_t>(s * (kStageBytesBT >> 4));
+        if (elect_one()) {
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            // the next 32-byte K slice is 2 units of 16 bytes further in the start-address field
+            umma_f8(acc, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+          }
+          umma_commit_addr(acc_full0 + s * 8);  // partial product ready for promotion; stage may be refilled
+        }
+        __syncwarp();
       }
     } else if (warp == kSignalWarp) {
       if constexpr (MULTI) {
