@@ -91,6 +91,29 @@ __device__ __forceinline__ bool mbar_wait_addr(uint32_t addr, uint32_t parity, u
   }
 }
 
+// The same wait for warps that are off the critical path: between polls the warp sleeps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns) {
+  const uint32_t addr = smem_addr(bar);
+  unsigned long long start = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) {
+      return true;
+    }
+    __nanosleep(100);
+    if ((spins & 63u) == 63u) {
+      const unsigned long long now = dev::global_timer_ns();
+      if (start == 0) {
+        start = now;
+      } else if (now - start > timeout_ns) {
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(smem_addr(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar)) : "memory");
@@ -208,6 +231,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   __shared__ __align__(8) uint64_t bar_full[kStagesT];
   __shared__ __align__(8) uint64_t bar_acc_full[kAccBuffersT];
   __shared__ __align__(8) uint64_t bar_acc_empty[kAccBuffersT];
+  __shared__ __align__(8) uint64_t bar_tile_stored[2];     // promotion warps -> publisher: tile is in memory
+  __shared__ __align__(8) uint64_t bar_tile_published[2];  // publisher -> promotion warps: slot may be reused
   __shared__ uint32_t s_tmem_base;
   __shared__ volatile int s_abort;
   __shared__ int s_barrier_ok;
@@ -225,6 +250,10 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int b = 0; b < kAccBuffersT; ++b) {
       mbar_init(&bar_acc_full[b], 1);
       mbar_init(&bar_acc_empty[b], kEpilogueWarps);  // one arrival per promotion warp
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bar_tile_stored[b], kEpilogueWarps * 32);
+      mbar_init(&bar_tile_published[b], 1);
     }
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -309,14 +338,28 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     } else if (warp == kSignalWarp) {
       if constexpr (MULTI) {
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-          // completes when all promotion threads have stored their part of tile t (they only arrive)
-          named_barrier(1, kEpilogueWarps * 32 + 32);
-          if (lane == 0 && !s_abort) {
+        // Tiles are handed over through a two-slot mbarrier pair (both waits bounded): the
+        // promotion warps may run at most two tiles ahead of the publisher.
+        uint32_t n = 0;
+        for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x, ++n) {
+          const uint32_t slot = n & 1u;
+          const uint32_t parity = (n >> 1) & 1u;
+          if (!mbar_wait_relaxed(&bar_tile_stored[slot], parity, comm.timeout_ns)) {
+            if (lane == 0) {
+              dev::report(comm, kStatusCopyTimeout, 0x400u + slot);
+              s_abort = 1;
+            }
+            break;
+          }
+          if (lane == 0) {
             const int owner = t % comm.world;
             uint32_t* flag = reinterpret_cast<uint32_t*>(p.ws_peers.ptr[owner] + kGemmWsFlagOffset) + t;
+            // release: the tile stores of all promotion threads (ordered before this by the
+            // barrier) are visible to every GPU before the owner can see the arrival
             asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+            mbar_arrive(&bar_tile_published[slot]);
           }
+          __syncwarp();
         }
       }
     }
@@ -326,15 +369,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int half = (warp - kEpilogueWarp0) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     uint32_t it = 0;
-    // Every tile ends with exactly one arrival per thread on the publisher's barrier, also after a
-    // timeout, so that the publisher warp (which can only wait on that barrier) always gets out.
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      if (s_abort) {
-        if constexpr (MULTI) {
-          asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
-        }
-        continue;
-      }
+    uint32_t tile_n = 0;
+    for (int t = blockIdx.x; t < total_tiles && !s_abort; t += gridDim.x, ++tile_n) {
       const int mt = t / tiles_n;
       const int nt = t % tiles_n;
       const int row = mt * BM + row_in_tile;
@@ -402,10 +438,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       }
       if (!ok) {
-        if constexpr (MULTI) {
-          asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
-        }
-        continue;
+        break;
       }
       // BF16 part-row of this tile into this rank's copy of the output (the partial product when
       // several ranks take part, the final result otherwise)
@@ -420,8 +453,18 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         dst[q] = v;
       }
       if constexpr (MULTI) {
-        // hand the stored tile to the publisher warp without waiting (arrive, not sync)
-        asm volatile("bar.arrive 1, %0;" ::"n"(kEpilogueWarps * 32 + 32) : "memory");
+        // hand the stored tile to the publisher warp; this only waits when the publisher is two
+        // tiles behind
+        const uint32_t slot = tile_n & 1u;
+        const uint32_t parity = (tile_n >> 1) & 1u;
+        if (!mbar_wait_relaxed(&bar_tile_published[slot], parity ^ 1u, comm.timeout_ns)) {
+          if (lane == 0) {
+            dev::report(comm, kStatusCopyTimeout, 0x500u + slot);
+            s_abort = 1;
+          }
+          break;
+        }
+        mbar_arrive(&bar_tile_stored[slot]);
       }
     }
   } else {

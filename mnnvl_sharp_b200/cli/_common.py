@@ -27,6 +27,11 @@ def time_steps(boot, comm, fn, iters: int, warmup: int = 3, graph: bool = False)
     """
     for _ in range(warmup):
         fn()
+    torch.cuda.synchronize()
+    # fail fast: a kernel that gave up waiting for a peer would do so again in every timed call
+    if not boot.all_true(comm.status().ok):
+        comm.raise_if_failed("warm-up")
+        raise RuntimeError("a device-side wait failed on another rank during warm-up")
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()

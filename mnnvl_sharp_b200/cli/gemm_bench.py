@@ -41,7 +41,7 @@ def main() -> int:
     p.add_argument("--graph", action="store_true")
     args = p.parse_args()
 
-    boot, comm = init_rank()
+    boot, comm = init_rank(wait_timeout_ms=1500)
     world, rank = comm.world, comm.rank
     m, n, k = args.m, args.n, args.k_local
     torch.manual_seed(100 + rank)
