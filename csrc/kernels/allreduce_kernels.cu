@@ -436,7 +436,9 @@ void launch_pull_kind(const DeviceComm& comm, void* data, std::size_t bytes, con
   const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
   auto go = [&](auto kernel, int u) {
     const std::size_t work = (per_rank + static_cast<std::size_t>(block) * u - 1) / (static_cast<std::size_t>(block) * u);
-    const int grid = resident_grid(kernel, block, 0, work, shape.grid > 0 ? shape.grid : kDefaultGridCap);
+    // a single rank only streams through its own memory: there the whole GPU is the right grid
+    const int cap = KIND == dev::kReduceLocalCopy ? 0 : kDefaultGridCap;
+    const int grid = resident_grid(kernel, block, 0, work, shape.grid > 0 ? shape.grid : cap);
     kernel<<<grid, block, 0, stream>>>(comm, static_cast<uint4*>(data), vectors, tail_words);
   };
   switch (unroll) {
