@@ -45,7 +45,7 @@ def parse_args():
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.01):
         super().__init__(daemon=True)
         self.index = index
         self.period = period_s
@@ -173,8 +173,22 @@ def run_ours(args) -> int:
         ms = timed_region(step, steps)
         if dtype == "e4m3":
             launches["timed"] = steps
+            # The timed region lasts a few milliseconds, too short for more than a sample or two of
+            # NVML: keep the same kernel running (untimed) for 0.4 s so that the clock record shows
+            # the state of the GPU under this load. All ranks do it; the kernels wait for each other.
+            t_end = time.time() + 0.4
+            keep_going = True
+            while keep_going:
+                for _ in range(10):
+                    step()
+                torch.cuda.synchronize()
+                keep_going = boot.all_true(time.time() < t_end)
+            if sampler is not None:
+                clocks = sampler.stop()
+                clocks["window"] = "timed region plus 0.4 s of the same kernel"
         results[dtype] = ms
-    clocks = sampler.stop() if sampler is not None else {}
+    if sampler is None:
+        clocks = {}
 
     # end to end through the public API: pinned host input -> device, all-reduce, result -> host
     dtype, backend = "e4m3", "legacy"
