@@ -63,7 +63,11 @@ def case_allreduce_seeded(comm, boot):
             # cancel make a distance in representable values meaningless; bound the absolute error instead
             good = m.max_abs_error <= (comm.world - 1) * 2.0 ** -11 * 6.0 * comm.world
         elif dtype == "e4m3" and backend == "legacy":
-            good = same and m.max_requantized_ulp_distance <= tol and m.switch_model_mismatches == 0
+            good = same and m.max_requantized_ulp_distance <= tol
+            if comm.world == 2:
+                # one add per element, so the exact sum is known and the result must be one of its two
+                # neighbours; with more ranks the f16 partial sums round and the bracket can be missed
+                good = good and m.switch_model_mismatches == 0
         else:
             good = same and m.max_requantized_ulp_distance <= tol
         detail.append((backend, dtype, m.max_requantized_ulp_distance, m.switch_model_mismatches, same))
