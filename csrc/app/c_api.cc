@@ -271,11 +271,17 @@ const char* msharp_run_cpu_only(int argc, const char* const* argv) {
 
 // ---------------------------------------------------------------------------- control plane
 void* msharp_bootstrap_connect(int rank, int world, const char* session, int timeout_ms) {
+  return msharp_bootstrap_connect_address(rank, world, session, nullptr, timeout_ms);
+}
+
+void* msharp_bootstrap_connect_address(int rank, int world, const char* session, const char* address,
+                                       int timeout_ms) {
   try {
     msharp::BootstrapOptions opt;
     opt.rank = rank;
     opt.world = world;
     opt.session = session != nullptr ? session : "default";
+    opt.address = address != nullptr ? address : "";
     opt.timeout_ms = timeout_ms;
     g_error.clear();
     return msharp::Bootstrap::connect(opt).release();
@@ -286,6 +292,8 @@ void* msharp_bootstrap_connect(int rank, int world, const char* session, int tim
 }
 
 void msharp_bootstrap_destroy(void* b) { delete static_cast<msharp::Bootstrap*>(b); }
+
+int msharp_bootstrap_can_pass_fds(void* b) { return static_cast<msharp::Bootstrap*>(b)->can_pass_fds() ? 1 : 0; }
 
 int msharp_bootstrap_barrier(void* b) {
   return guarded([&] { static_cast<msharp::Bootstrap*>(b)->barrier(); });

@@ -3,6 +3,11 @@
 // Started without RANK / WORLD_SIZE in the environment it is the launcher: it reads the rack
 // inventory, builds the rank plan and starts one copy of itself per selected GPU on this host
 // (the job that mpirun + rankfile do for the reference project, scripts/run_mnnvl_sharp.sh:252-263).
+// When the plan names several hosts, the same command line is started once on each of them
+// (by hand, by a scheduler, or by the Python launcher over ssh): every copy starts only the
+// ranks whose tray label is this host's (MNNVL_HOST_LABEL, else the short host name), and all
+// ranks meet at rank 0's TCP control socket (--hub-address / MSHARP_HUB_ADDR, default: the
+// control hostname of rank 0's tray, port MSHARP_HUB_PORT or 29431).
 // Started with them (by its own launcher, by torchrun, or by any other process manager) it is
 // one rank. Exit codes as in the reference's main (src/main.cc:491-505): 0 ok, 2 result check
 // failed, 1 error; errors are printed as "rank R error: ...".
@@ -12,12 +17,14 @@
 #include <exception>
 #include <iostream>
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
 #include "msharp/bootstrap.h"
 #include "msharp/config.h"
 #include "msharp/driver_api.h"
+#include "msharp/fake_driver.h"
 #include "msharp/rack.h"
 #include "msharp/runner.h"
 
@@ -39,6 +46,33 @@ std::string self_path(const char* argv0) {
   return argv0;
 }
 
+std::string env_or(const char* name, const std::string& fallback) {
+  const char* v = std::getenv(name);
+  return v != nullptr && *v != '\0' ? std::string(v) : fallback;
+}
+
+std::string short_host_name() {
+  char buf[256] = {0};
+  if (gethostname(buf, sizeof(buf) - 1) != 0) {
+    return "localhost";
+  }
+  return msharp::normalize_host_label(buf);
+}
+
+// MSHARP_DRIVER=fake runs the host side of a rank (plan, topology checks, control plane, memory
+// set-up, canary, report) against the host-memory stand-in for the driver; only --init-only runs
+// that way. It exists so that launch and multi-host logic can be exercised on machines without GPUs.
+const msharp::DriverApi& chosen_driver() {
+  if (env_or("MSHARP_DRIVER", "real") != "fake") {
+    return msharp::real_driver();
+  }
+  msharp::fake_driver_reset(8);
+  if (env_or("MSHARP_FAKE_FABRIC", "0") == "1") {
+    msharp::fake_driver_set_attribute(CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED, 1);
+  }
+  return msharp::fake_driver();
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -55,7 +89,6 @@ int main(int argc, char** argv) {
     if (!launched_as_rank()) {
       const msharp::RackConfig rack = msharp::RackConfig::load(cfg.rack_config_path);
       const int world = cfg.rank_count.value_or(static_cast<int>(rack.available_rank_count()));
-      msharp::build_rank_plan(rack, world, cfg.rank_selection);  // fail early on a bad plan
       std::vector<std::string> args;
       args.push_back(self_path(argv[0]));
       for (int i = 1; i < argc; ++i) {
@@ -65,15 +98,40 @@ int main(int argc, char** argv) {
         args.emplace_back("--rank-count");
         args.emplace_back(std::to_string(world));
       }
-      const std::string session = cfg.session.empty() ? "pid" + std::to_string(getpid()) : cfg.session;
-      return msharp::spawn_local_ranks(args, world, session);
+      const msharp::RankPlan plan = msharp::build_rank_plan(rack, world, cfg.rank_selection);
+      if (plan.slot_counts_by_host().size() <= 1) {
+        const std::string session = cfg.session.empty() ? "pid" + std::to_string(getpid()) : cfg.session;
+        return msharp::spawn_local_ranks(args, world, session);
+      }
+      // Several hosts: start this host's share and point everyone at rank 0's TCP socket.
+      const std::string label = msharp::normalize_host_label(env_or("MNNVL_HOST_LABEL", short_host_name()));
+      std::vector<int> mine;
+      for (int r = 0; r < plan.size(); ++r) {
+        if (msharp::normalize_host_label(plan.target(r).host_label) == label) {
+          mine.push_back(r);
+        }
+      }
+      if (mine.empty()) {
+        throw std::runtime_error("the plan spans several hosts and none of its ranks is on this host ('" + label +
+                                 "'); set MNNVL_HOST_LABEL to this host's tray label");
+      }
+      std::string hub = !cfg.hub_address.empty() ? cfg.hub_address : env_or("MSHARP_HUB_ADDR", "");
+      if (hub.empty()) {
+        hub = plan.target(0).control_hostname + ":" + env_or("MSHARP_HUB_PORT", "29431");
+      }
+      // every host must arrive at the same name without talking to the others
+      const std::string session = cfg.session.empty() ? "rack" + std::to_string(world) : cfg.session;
+      return msharp::spawn_host_ranks(args, world, session, mine, hub);
     }
     msharp::BootstrapOptions opt = msharp::Bootstrap::options_from_env();
     if (!cfg.session.empty()) {
       opt.session = cfg.session;
     }
+    if (!cfg.hub_address.empty()) {
+      opt.address = cfg.hub_address;
+    }
     comm = msharp::Bootstrap::connect(opt);
-    return msharp::run_rank(cfg, *comm, msharp::real_driver(), std::cout);
+    return msharp::run_rank(cfg, *comm, chosen_driver(), std::cout);
   } catch (const std::exception& ex) {
     std::cerr << "rank " << rank << " error: " << ex.what() << "\n";
     if (comm) {

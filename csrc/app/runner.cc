@@ -89,9 +89,18 @@ void agree_on_device_status(RankRun& run, const char* what) {
 void canary_smoke_test(RankRun& run) {
   const TraceRange trace("canary_smoke_test");
   const int world = run.rank.world_size;
-  launch_canary_write(static_cast<uint32_t*>(run.input_ptr()), run.rank.world_rank, run.stream);
-  launch_alias_fence(run.stream);
-  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  if (run.api.is_fake) {
+    // no device: the host writes this rank's words through its own mapping
+    uint32_t mine[kCanaryWords];
+    for (int i = 0; i < kCanaryWords; ++i) {
+      mine[i] = 0xC0010000u | ((static_cast<uint32_t>(run.rank.world_rank) & 0xffu) << 8) | static_cast<uint32_t>(i);
+    }
+    run.mem->copy_from_host(run.rank.world_rank, run.mem->input_offset, mine, sizeof(mine));
+  } else {
+    launch_canary_write(static_cast<uint32_t*>(run.input_ptr()), run.rank.world_rank, run.stream);
+    launch_alias_fence(run.stream);
+    MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  }
   run.comm.barrier();
   // host view: copy the canary of every slot (own and peers) through the unicast mappings
   for (int slot = 0; slot < world; ++slot) {
@@ -106,6 +115,10 @@ void canary_smoke_test(RankRun& run) {
         throw std::runtime_error(os.str());
       }
     }
+  }
+  if (run.api.is_fake) {
+    run.comm.barrier();
+    return;
   }
   // device view: a kernel reads every slot after a device barrier
   PeerPointers slots{};
@@ -206,8 +219,14 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   const char* label_env = std::getenv("MNNVL_HOST_LABEL");
   RankRun run{cfg, comm, api, {}, {}, nullptr, nullptr, nullptr, nullptr, nullptr, Dtype::kE4M3, 0, {}, {}, {}};
   run.rank = discover_rank_info(comm.rank(), world, rack, plan, label_env != nullptr ? label_env : "");
-  MSHARP_CUDA(cudaSetDevice(run.rank.gpu_ordinal));
-  MSHARP_CUDA(cudaFree(nullptr));  // creates the primary context that the driver calls below use
+  const bool fake = api.is_fake;
+  if (fake && !cfg.init_only) {
+    throw std::runtime_error("the host-memory driver stand-in runs --init-only only (there is no device to reduce on)");
+  }
+  if (!fake) {
+    MSHARP_CUDA(cudaSetDevice(run.rank.gpu_ordinal));
+    MSHARP_CUDA(cudaFree(nullptr));  // creates the primary context that the driver calls below use
+  }
   run.caps = query_capabilities(api, &run.rank);
   if (!cfg.no_pin) {
     pin_thread_to_numa(run.rank.host_numa_id);
@@ -222,9 +241,11 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   run.shape.block = cfg.block;
   run.shape.unroll = cfg.unroll;
 
-  MSHARP_CUDA(cudaStreamCreateWithFlags(&run.stream, cudaStreamNonBlocking));
-  MSHARP_CUDA(cudaEventCreate(&run.start));
-  MSHARP_CUDA(cudaEventCreate(&run.stop));
+  if (!fake) {
+    MSHARP_CUDA(cudaStreamCreateWithFlags(&run.stream, cudaStreamNonBlocking));
+    MSHARP_CUDA(cudaEventCreate(&run.start));
+    MSHARP_CUDA(cudaEventCreate(&run.stop));
+  }
 
   SymmOptions base;
   base.handle_type = cfg.handle_type;
@@ -355,7 +376,9 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   }
 
   // Teardown in order on every path: no rank unmaps while a peer's kernel may still run.
-  cudaStreamSynchronize(run.stream);
+  if (!fake) {
+    cudaStreamSynchronize(run.stream);
+  }
   if (failure.empty()) {
     try {
       comm.barrier();
@@ -369,9 +392,11 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   if (run.ctx) {
     run.ctx->destroy(nullptr);
   }
-  cudaEventDestroy(run.stop);
-  cudaEventDestroy(run.start);
-  cudaStreamDestroy(run.stream);
+  if (!fake) {
+    cudaEventDestroy(run.stop);
+    cudaEventDestroy(run.start);
+    cudaStreamDestroy(run.stream);
+  }
   if (!failure.empty()) {
     throw std::runtime_error(failure);
   }

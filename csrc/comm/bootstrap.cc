@@ -1,5 +1,8 @@
 #include "msharp/bootstrap.h"
 
+#include <netdb.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
 #include <poll.h>
 #include <sys/socket.h>
 #include <sys/un.h>
@@ -74,6 +77,43 @@ sockaddr_un abstract_address(const std::string& session, socklen_t* len) {
   std::memcpy(addr.sun_path + 1, name.data(), name.size());
   *len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + name.size());
   return addr;
+}
+
+// 32-bit FNV-1a of the session name: sent in the greeting so that a stranger on the same TCP port
+// (another job, a port scanner) is turned away instead of being taken for a rank.
+uint32_t session_tag(const std::string& session) {
+  uint32_t h = 2166136261u;
+  for (unsigned char c : session) {
+    h = (h ^ c) * 16777619u;
+  }
+  return h;
+}
+
+// "host:port" or "[v6-literal]:port" -> (host, port text).
+void split_address(const std::string& address, std::string* host, std::string* port) {
+  const std::size_t colon = address.rfind(':');
+  if (colon == std::string::npos || colon == 0 || colon + 1 >= address.size()) {
+    throw BootstrapError("bootstrap: address must be host:port, got '" + address + "'");
+  }
+  *host = address.substr(0, colon);
+  *port = address.substr(colon + 1);
+  if (host->size() >= 2 && host->front() == '[' && host->back() == ']') {
+    *host = host->substr(1, host->size() - 2);
+  }
+  for (char c : *port) {
+    if (c < '0' || c > '9') {
+      throw BootstrapError("bootstrap: port must be a number in '" + address + "'");
+    }
+  }
+  const long value = std::strtol(port->c_str(), nullptr, 10);
+  if (value < 1 || value > 65535) {
+    throw BootstrapError("bootstrap: port out of range in '" + address + "'");
+  }
+}
+
+void set_no_delay(int fd) {
+  const int one = 1;
+  ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
 }
 
 // Wait until `fd` is readable / writable; false on timeout.
@@ -233,12 +273,14 @@ class SoloBootstrap final : public Bootstrap {
   void broadcast(void*, std::size_t, int) override {}
   std::vector<int> allgather_fd(int fd) override { return {fd >= 0 ? ::dup(fd) : -1}; }
   int broadcast_fd(int fd, int) override { return fd >= 0 ? ::dup(fd) : -1; }
+  bool can_pass_fds() const override { return true; }
   void abort(const std::string&) noexcept override {}
 };
 
 class HubBootstrap final : public Bootstrap {
  public:
-  explicit HubBootstrap(const BootstrapOptions& opt) : opt_(opt) {
+  explicit HubBootstrap(const BootstrapOptions& opt)
+      : opt_(opt), tcp_(!opt.address.empty()), tag_(session_tag(opt.session)) {
     if (opt.rank < 0 || opt.rank >= opt.world) {
       throw BootstrapError("bootstrap: rank " + std::to_string(opt.rank) + " is outside world size " +
                            std::to_string(opt.world));
@@ -281,7 +323,13 @@ class HubBootstrap final : public Bootstrap {
     std::memcpy(buffer, all.data() + bytes * static_cast<std::size_t>(root), bytes);
   }
 
+  bool can_pass_fds() const override { return !tcp_; }
+
   std::vector<int> allgather_fd(int fd) override {
+    if (tcp_) {
+      throw BootstrapError("bootstrap: file descriptors cannot be passed over TCP; memory that is shared between hosts "
+                           "needs fabric handles");
+    }
     const uint32_t seq = ++seq_;
     check_not_aborted();
     const Deadline deadline(opt_.timeout_ms);
@@ -469,16 +517,71 @@ class HubBootstrap final : public Bootstrap {
     }
   }
 
+  int open_listener() {
+    if (!tcp_) {
+      socklen_t len = 0;
+      const sockaddr_un addr = abstract_address(opt_.session, &len);
+      const int fd = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+      if (fd < 0) {
+        throw BootstrapError(std::string("bootstrap: socket failed: ") + std::strerror(errno));
+      }
+      if (::bind(fd, reinterpret_cast<const sockaddr*>(&addr), len) != 0) {
+        const std::string why = std::strerror(errno);
+        ::close(fd);
+        throw BootstrapError("bootstrap: cannot bind session '" + opt_.session + "': " + why);
+      }
+      return fd;
+    }
+    // TCP: every interface, the port of the address. The host part only matters to the ranks that connect.
+    std::string host;
+    std::string port;
+    split_address(opt_.address, &host, &port);
+    addrinfo hints;
+    std::memset(&hints, 0, sizeof(hints));
+    hints.ai_family = AF_UNSPEC;
+    hints.ai_socktype = SOCK_STREAM;
+    hints.ai_flags = AI_PASSIVE | AI_NUMERICSERV;
+    addrinfo* list = nullptr;
+    const int rc = ::getaddrinfo(nullptr, port.c_str(), &hints, &list);
+    if (rc != 0) {
+      throw BootstrapError(std::string("bootstrap: cannot resolve a listening address: ") + gai_strerror(rc));
+    }
+    std::string why = "no usable address";
+    int fd = -1;
+    // Prefer an IPv6 wildcard socket that also takes IPv4 (dual stack); fall back to IPv4.
+    for (int pass = 0; pass < 2 && fd < 0; ++pass) {
+      for (addrinfo* ai = list; ai != nullptr && fd < 0; ai = ai->ai_next) {
+        if ((pass == 0) != (ai->ai_family == AF_INET6)) {
+          continue;
+        }
+        const int s = ::socket(ai->ai_family, ai->ai_socktype | SOCK_CLOEXEC, ai->ai_protocol);
+        if (s < 0) {
+          why = std::strerror(errno);
+          continue;
+        }
+        const int one = 1;
+        const int zero = 0;
+        ::setsockopt(s, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+        if (ai->ai_family == AF_INET6) {
+          ::setsockopt(s, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof(zero));
+        }
+        if (::bind(s, ai->ai_addr, ai->ai_addrlen) != 0) {
+          why = std::strerror(errno);
+          ::close(s);
+          continue;
+        }
+        fd = s;
+      }
+    }
+    ::freeaddrinfo(list);
+    if (fd < 0) {
+      throw BootstrapError("bootstrap: cannot listen on port " + port + ": " + why);
+    }
+    return fd;
+  }
+
   void listen_and_accept() {
-    socklen_t len = 0;
-    const sockaddr_un addr = abstract_address(opt_.session, &len);
-    listener_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
-    if (listener_ < 0) {
-      throw BootstrapError(std::string("bootstrap: socket failed: ") + std::strerror(errno));
-    }
-    if (::bind(listener_, reinterpret_cast<const sockaddr*>(&addr), len) != 0) {
-      throw BootstrapError("bootstrap: cannot bind session '" + opt_.session + "': " + std::strerror(errno));
-    }
+    listener_ = open_listener();
     if (::listen(listener_, opt_.world + 8) != 0) {
       throw BootstrapError(std::string("bootstrap: listen failed: ") + std::strerror(errno));
     }
@@ -502,12 +605,15 @@ class HubBootstrap final : public Bootstrap {
       if (fd < 0) {
         continue;
       }
+      if (tcp_) {
+        set_no_delay(fd);
+      }
       Header h;
       const Deadline hello_deadline(std::min(opt_.timeout_ms, 2000));
       if (read_exact(fd, &h, sizeof(h), hello_deadline) != IoStatus::kOk || h.magic != kMagic || h.op != kHello ||
-          h.rank <= 0 || h.rank >= opt_.world || h.bytes != static_cast<uint64_t>(opt_.world) ||
+          h.seq != tag_ || h.rank <= 0 || h.rank >= opt_.world || h.bytes != static_cast<uint64_t>(opt_.world) ||
           peers_[static_cast<std::size_t>(h.rank)] >= 0) {
-        ::close(fd);  // stranger, duplicate rank, or a rank that disagrees on the world size
+        ::close(fd);  // stranger, other session, duplicate rank, or a rank that disagrees on the world size
         continue;
       }
       peers_[static_cast<std::size_t>(h.rank)] = fd;
@@ -518,6 +624,7 @@ class HubBootstrap final : public Bootstrap {
     for (int r = 1; r < opt_.world; ++r) {
       Header h;
       h.op = kHello;
+      h.seq = tag_;
       h.rank = 0;
       h.bytes = static_cast<uint64_t>(opt_.world);
       guard(write_exact(peers_[static_cast<std::size_t>(r)], &h, sizeof(h), go), r, kHello);
@@ -536,35 +643,75 @@ class HubBootstrap final : public Bootstrap {
     }
   }
 
-  void connect_to_hub() {
-    socklen_t len = 0;
-    const sockaddr_un addr = abstract_address(opt_.session, &len);
-    const Deadline deadline(opt_.timeout_ms);
-    for (;;) {
-      hub_ = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
-      if (hub_ < 0) {
+  // One connection attempt; -1 when rank 0 is not there (yet).
+  int try_connect() {
+    if (!tcp_) {
+      socklen_t len = 0;
+      const sockaddr_un addr = abstract_address(opt_.session, &len);
+      const int fd = ::socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+      if (fd < 0) {
         throw BootstrapError(std::string("bootstrap: socket failed: ") + std::strerror(errno));
       }
-      if (::connect(hub_, reinterpret_cast<const sockaddr*>(&addr), len) == 0) {
+      if (::connect(fd, reinterpret_cast<const sockaddr*>(&addr), len) == 0) {
+        return fd;
+      }
+      ::close(fd);
+      return -1;
+    }
+    std::string host;
+    std::string port;
+    split_address(opt_.address, &host, &port);
+    addrinfo hints;
+    std::memset(&hints, 0, sizeof(hints));
+    hints.ai_family = AF_UNSPEC;
+    hints.ai_socktype = SOCK_STREAM;
+    hints.ai_flags = AI_NUMERICSERV;
+    addrinfo* list = nullptr;
+    if (::getaddrinfo(host.c_str(), port.c_str(), &hints, &list) != 0) {
+      return -1;  // the name may not resolve yet; the caller retries until its deadline
+    }
+    int fd = -1;
+    for (addrinfo* ai = list; ai != nullptr && fd < 0; ai = ai->ai_next) {
+      const int s = ::socket(ai->ai_family, ai->ai_socktype | SOCK_CLOEXEC, ai->ai_protocol);
+      if (s < 0) {
+        continue;
+      }
+      if (::connect(s, ai->ai_addr, ai->ai_addrlen) == 0) {
+        set_no_delay(s);
+        fd = s;
+      } else {
+        ::close(s);
+      }
+    }
+    ::freeaddrinfo(list);
+    return fd;
+  }
+
+  void connect_to_hub() {
+    const Deadline deadline(opt_.timeout_ms);
+    for (;;) {
+      hub_ = try_connect();
+      if (hub_ >= 0) {
         break;
       }
-      ::close(hub_);
-      hub_ = -1;
       if (deadline.expired()) {
-        throw BootstrapError("bootstrap: rank " + std::to_string(opt_.rank) + ": timed out connecting to rank 0 (session '" +
-                             opt_.session + "')");
+        throw BootstrapError("bootstrap: rank " + std::to_string(opt_.rank) + ": timed out connecting to rank 0 (" +
+                             (tcp_ ? "address " + opt_.address + ", " : std::string()) + "session '" + opt_.session + "')");
       }
-      std::this_thread::sleep_for(std::chrono::milliseconds(10));
+      std::this_thread::sleep_for(std::chrono::milliseconds(tcp_ ? 50 : 10));
     }
     Header h;
     h.op = kHello;
+    h.seq = tag_;
     h.rank = opt_.rank;
     h.bytes = static_cast<uint64_t>(opt_.world);
     guard(write_exact(hub_, &h, sizeof(h), deadline), 0, kHello);
-    expect_header(0, kHello, 0, static_cast<uint64_t>(opt_.world), deadline);
+    expect_header(0, kHello, tag_, static_cast<uint64_t>(opt_.world), deadline);
   }
 
   BootstrapOptions opt_;
+  bool tcp_ = false;
+  uint32_t tag_ = 0;
   int listener_ = -1;
   int hub_ = -1;
   std::vector<int> peers_;
@@ -631,6 +778,9 @@ BootstrapOptions Bootstrap::options_from_env() {
     opt.session = s;
   } else if (const char* p = std::getenv("MASTER_PORT"); p != nullptr && *p != '\0') {
     opt.session = std::string("port") + p;
+  }
+  if (const char* a = std::getenv("MSHARP_HUB_ADDR"); a != nullptr && *a != '\0') {
+    opt.address = a;
   }
   opt.timeout_ms = env_int("MSHARP_BOOTSTRAP_TIMEOUT_MS", opt.timeout_ms);
   return opt;

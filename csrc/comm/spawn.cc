@@ -14,11 +14,21 @@
 namespace msharp {
 
 int spawn_local_ranks(const std::vector<std::string>& argv, int world, const std::string& session) {
-  if (argv.empty() || world <= 0) {
+  std::vector<int> all;
+  for (int rank = 0; rank < world; ++rank) {
+    all.push_back(rank);
+  }
+  return spawn_host_ranks(argv, world, session, all, "");
+}
+
+int spawn_host_ranks(const std::vector<std::string>& argv, int world, const std::string& session,
+                     const std::vector<int>& global_ranks, const std::string& hub_address) {
+  if (argv.empty() || world <= 0 || global_ranks.empty()) {
     throw std::runtime_error("spawn: nothing to run");
   }
   std::vector<pid_t> children;
-  for (int rank = 0; rank < world; ++rank) {
+  for (std::size_t local = 0; local < global_ranks.size(); ++local) {
+    const int rank = global_ranks[local];
     const pid_t pid = fork();
     if (pid < 0) {
       const std::string why = std::strerror(errno);
@@ -29,9 +39,12 @@ int spawn_local_ranks(const std::vector<std::string>& argv, int world, const std
     }
     if (pid == 0) {
       setenv("RANK", std::to_string(rank).c_str(), 1);
-      setenv("LOCAL_RANK", std::to_string(rank).c_str(), 1);
+      setenv("LOCAL_RANK", std::to_string(local).c_str(), 1);
       setenv("WORLD_SIZE", std::to_string(world).c_str(), 1);
       setenv("MSHARP_SESSION", session.c_str(), 1);
+      if (!hub_address.empty()) {
+        setenv("MSHARP_HUB_ADDR", hub_address.c_str(), 1);
+      }
       std::vector<char*> args;
       for (const auto& a : argv) {
         args.push_back(const_cast<char*>(a.c_str()));

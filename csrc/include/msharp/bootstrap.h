@@ -1,9 +1,12 @@
-// Control plane for one process per GPU on a single host: a star of Unix-domain stream
-// sockets with rank 0 as the hub. It carries what the reference project sends over MPI
-// (64-byte memory handles, barriers, tiny reductions, the final status; call sites listed in
+// Control plane for one process per GPU: a star of stream sockets with rank 0 as the hub.
+// On one host the sockets are Unix-domain sockets in the abstract namespace; when the job spans
+// hosts (BootstrapOptions::address set) they are TCP connections to rank 0. It carries what the
+// reference project sends over MPI (64-byte memory handles, barriers, tiny reductions, the final status; call sites listed in
 // the reference at src/runtime.cc:158-162,237,319, src/fabric_memory.cc:111-169 and
 // src/main.cc:91-139,195,478) and, in addition, passes POSIX file descriptors between
 // processes with SCM_RIGHTS, which MPI cannot do and which the POSIX-FD memory handles need.
+// Descriptors cannot cross hosts: over TCP can_pass_fds() is false and the memory layer uses
+// fabric handles (plain 64-byte blobs), as the reference does.
 //
 // Every call is collective and must be made by all ranks in the same order. Every wait has a
 // deadline; on expiry, on a closed peer, or when any rank calls abort(), all ranks that are
@@ -29,6 +32,10 @@ struct BootstrapOptions {
   int world = 1;
   std::string session = "default";  // ranks of one job share it; becomes an abstract socket name
   int timeout_ms = 30000;           // deadline of connect and of every collective
+  // Empty: Unix-domain sockets (single host). "host:port": rank 0 listens on that TCP port on
+  // all interfaces and every other rank connects to host:port; the session name is checked in
+  // the greeting so that two jobs that were given the same port by mistake do not mix.
+  std::string address;
 };
 
 class Bootstrap {
@@ -46,6 +53,8 @@ class Bootstrap {
   // duplicate of its own). Ranks that have nothing to share pass -1 and receive -1 in that place.
   virtual std::vector<int> allgather_fd(int fd) = 0;
   virtual int broadcast_fd(int fd, int root) = 0;
+  // False when the transport cannot carry descriptors (TCP); allgather_fd / broadcast_fd then throw.
+  virtual bool can_pass_fds() const = 0;
   // Tell every other rank that this rank failed; their current or next collective throws.
   virtual void abort(const std::string& reason) noexcept = 0;
 
@@ -58,7 +67,8 @@ class Bootstrap {
   int broadcast_int(int value, int root);
 
   static std::unique_ptr<Bootstrap> connect(const BootstrapOptions& options);
-  // Options from RANK / WORLD_SIZE / MSHARP_SESSION (or MASTER_PORT) in the environment.
+  // Options from RANK / WORLD_SIZE / MSHARP_SESSION (or MASTER_PORT) / MSHARP_HUB_ADDR
+  // (host:port, selects TCP) / MSHARP_BOOTSTRAP_TIMEOUT_MS in the environment.
   static BootstrapOptions options_from_env();
 };
 

@@ -46,6 +46,9 @@ const char* msharp_run_cpu_only(int argc, const char* const* argv);
 
 // ---- control plane
 void* msharp_bootstrap_connect(int rank, int world, const char* session, int timeout_ms);
+// address: NULL or "" for Unix-domain sockets on one host, "host:port" for TCP across hosts.
+void* msharp_bootstrap_connect_address(int rank, int world, const char* session, const char* address, int timeout_ms);
+int msharp_bootstrap_can_pass_fds(void* bootstrap);
 void msharp_bootstrap_destroy(void* bootstrap);
 int msharp_bootstrap_barrier(void* bootstrap);
 int msharp_bootstrap_allgather(void* bootstrap, const void* send, void* recv, size_t bytes_per_rank);

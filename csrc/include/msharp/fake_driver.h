@@ -4,6 +4,10 @@
 // process and mapped there; address reservations are PROT_NONE mmaps and cuMemMap places the
 // file at the reserved address, so "device pointers" are ordinary host pointers that the
 // canary check can read. Multicast objects are bookkeeping only (nothing replicates stores).
+// With CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED set to 1, allocations that ask for
+// fabric handles are named shared-memory objects and the 64-byte handle carries the name, so
+// the handle exchange of a multi-host job (bytes over TCP, no descriptors) can be run among
+// processes of one machine.
 // Every call is logged, and a chosen call can be made to fail with a chosen CUresult: that is
 // how failure handling of the symmetric-memory set-up is exercised without touching a GPU.
 #pragma once

@@ -26,4 +26,10 @@ int run_cpu_only(const Config& cfg, std::ostream& out);
 // terminated by pid), else 0.
 int spawn_local_ranks(const std::vector<std::string>& argv, int world, const std::string& session);
 
+// The same for the part of a multi-host job that runs on this host: one child per entry of
+// `global_ranks` (RANK = that entry, LOCAL_RANK = its index in the list), WORLD_SIZE = world,
+// and MSHARP_HUB_ADDR = hub_address so that every rank reaches rank 0 over TCP.
+int spawn_host_ranks(const std::vector<std::string>& argv, int world, const std::string& session,
+                     const std::vector<int>& global_ranks, const std::string& hub_address);
+
 }  // namespace msharp

@@ -17,6 +17,8 @@ struct Handle {
   bool multicast = false;
   size_t size = 0;
   int fd = -1;
+  std::string shm_name;  // set when the backing is a named shared-memory object (fabric handles)
+  bool owns_name = false;
   int device = 0;
   std::vector<int> added_devices;
   int bindings = 0;
@@ -58,6 +60,43 @@ State& state() {
 }
 
 constexpr size_t kGranularity = 2u << 20;
+
+// Backing store of one allocation. Allocations that ask for fabric handles get a named POSIX
+// shared-memory object, whose name is the content of the 64-byte "fabric handle": any process
+// of this machine can open it by name, which stands in for what IMEX does between hosts. All
+// others get an anonymous memfd that is shared by passing the descriptor.
+int create_backing(size_t size, bool named, uint64_t id, const char* suffix, std::string* name) {
+  int fd = -1;
+  if (named) {
+    *name = "/msharp-fake-" + std::to_string(getpid()) + "-" + std::to_string(id) + suffix;
+    fd = shm_open(name->c_str(), O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+  } else {
+    fd = memfd_create("msharp-fake", MFD_CLOEXEC);
+  }
+  if (fd < 0) {
+    return -1;
+  }
+  if (ftruncate(fd, static_cast<off_t>(size)) != 0) {
+    close(fd);
+    if (named) {
+      shm_unlink(name->c_str());
+    }
+    return -1;
+  }
+  return fd;
+}
+
+void release_backing(Handle& h) {
+  close(h.fd);
+  if (h.owns_name) {
+    shm_unlink(h.shm_name.c_str());
+  }
+}
+
+bool fabric_enabled() {
+  auto it = state().attributes.find(static_cast<int>(CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED));
+  return it != state().attributes.end() && it->second != 0;
+}
 
 // Log the call; returns the injected failure if one is due.
 CUresult enter(const std::string& name, const std::string& detail = "") {
@@ -168,16 +207,17 @@ CUresult f_MemCreate(CUmemGenericAllocationHandle* out, size_t size, const CUmem
   if (size == 0 || size % kGranularity != 0) {
     return CUDA_ERROR_INVALID_VALUE;
   }
-  const int fd = memfd_create("msharp-fake", MFD_CLOEXEC);
-  if (fd < 0 || ftruncate(fd, static_cast<off_t>(size)) != 0) {
-    if (fd >= 0) {
-      close(fd);
-    }
-    return CUDA_ERROR_OUT_OF_MEMORY;
+  const bool named = (prop->requestedHandleTypes & CU_MEM_HANDLE_TYPE_FABRIC) != 0;
+  if (named && !fabric_enabled()) {
+    return CUDA_ERROR_NOT_SUPPORTED;
   }
   Handle h;
+  h.fd = create_backing(size, named, state().next_handle, "", &h.shm_name);
+  if (h.fd < 0) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  h.owns_name = named;
   h.size = size;
-  h.fd = fd;
   h.device = prop->location.id;
   *out = state().next_handle++;
   state().handles[*out] = h;
@@ -190,7 +230,7 @@ CUresult f_MemRelease(CUmemGenericAllocationHandle handle) {
   if (it == state().handles.end()) {
     return CUDA_ERROR_INVALID_HANDLE;
   }
-  close(it->second.fd);
+  release_backing(it->second);
   state().handles.erase(it);
   return CUDA_SUCCESS;
 }
@@ -201,6 +241,15 @@ CUresult f_MemExport(void* shareable, CUmemGenericAllocationHandle handle, CUmem
   auto it = state().handles.find(handle);
   if (it == state().handles.end()) {
     return CUDA_ERROR_INVALID_HANDLE;
+  }
+  if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
+    if (!fabric_enabled() || it->second.shm_name.empty() || it->second.shm_name.size() >= sizeof(CUmemFabricHandle)) {
+      return CUDA_ERROR_NOT_SUPPORTED;
+    }
+    auto* blob = static_cast<CUmemFabricHandle*>(shareable);
+    std::memset(blob, 0, sizeof(*blob));
+    std::memcpy(blob->data, it->second.shm_name.data(), it->second.shm_name.size());
+    return CUDA_SUCCESS;
   }
   if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
     return CUDA_ERROR_NOT_SUPPORTED;
@@ -215,6 +264,32 @@ CUresult f_MemExport(void* shareable, CUmemGenericAllocationHandle handle, CUmem
 
 CUresult f_MemImport(CUmemGenericAllocationHandle* out, void* os_handle, CUmemAllocationHandleType type) {
   FAKE_ENTER("cuMemImportFromShareableHandle", "type=" + std::to_string(type));
+  if (type == CU_MEM_HANDLE_TYPE_FABRIC) {
+    if (!fabric_enabled()) {
+      return CUDA_ERROR_NOT_SUPPORTED;
+    }
+    const auto* blob = static_cast<const CUmemFabricHandle*>(os_handle);
+    const std::string name(reinterpret_cast<const char*>(blob->data),
+                           strnlen(reinterpret_cast<const char*>(blob->data), sizeof(blob->data)));
+    if (name.rfind("/msharp-fake-", 0) != 0) {
+      return CUDA_ERROR_INVALID_VALUE;  // truncated or foreign blob
+    }
+    Handle h;
+    h.fd = shm_open(name.c_str(), O_RDWR | O_CLOEXEC, 0600);
+    struct stat named_st;
+    if (h.fd < 0 || fstat(h.fd, &named_st) != 0) {
+      if (h.fd >= 0) {
+        close(h.fd);
+      }
+      return CUDA_ERROR_INVALID_VALUE;
+    }
+    h.size = static_cast<size_t>(named_st.st_size);
+    h.shm_name = name;
+    h.multicast = name.find("-mc") != std::string::npos;
+    *out = state().next_handle++;
+    state().handles[*out] = h;
+    return CUDA_SUCCESS;
+  }
   if (type != CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) {
     return CUDA_ERROR_NOT_SUPPORTED;
   }
@@ -314,14 +389,19 @@ CUresult f_MulticastCreate(CUmemGenericAllocationHandle* out, const CUmulticastO
   if (prop->numDevices < 2 || prop->size == 0 || prop->size % kGranularity != 0) {
     return CUDA_ERROR_INVALID_VALUE;  // the real driver also refuses single-device objects
   }
-  const int fd = memfd_create("msharp-fake-mc", MFD_CLOEXEC);
-  if (fd < 0 || ftruncate(fd, static_cast<off_t>(prop->size)) != 0) {
-    return CUDA_ERROR_OUT_OF_MEMORY;
+  const bool named = (prop->handleTypes & CU_MEM_HANDLE_TYPE_FABRIC) != 0;
+  if (named && !fabric_enabled()) {
+    return CUDA_ERROR_NOT_SUPPORTED;
   }
   Handle h;
+  // the "-mc" mark in the name tells an importer what it got
+  h.fd = create_backing(prop->size, named, state().next_handle, "-mc", &h.shm_name);
+  if (h.fd < 0) {
+    return CUDA_ERROR_OUT_OF_MEMORY;
+  }
+  h.owns_name = named;
   h.multicast = true;
   h.size = prop->size;
-  h.fd = fd;
   *out = state().next_handle++;
   state().handles[*out] = h;
   return CUDA_SUCCESS;
@@ -443,7 +523,7 @@ void fake_driver_reset(int device_count) {
     munmap(r.second.raw, r.second.raw_size);
   }
   for (auto& h : s.handles) {
-    close(h.second.fd);
+    release_backing(h.second);
   }
   s.mappings.clear();
   s.reservations.clear();

@@ -91,8 +91,11 @@ void SymmetricMemory::build(Bootstrap& comm, const SymmOptions& opt) {
   // ---- which handle type
   CUmemAllocationHandleType handle_type = CU_MEM_HANDLE_TYPE_NONE;
   if (!solo) {
+    // File descriptors travel only between processes of one host; a control plane that spans hosts
+    // (TCP) leaves fabric handles as the only way to share memory, as in the reference.
+    const bool fds_usable = opt.posix_fd_supported && comm.can_pass_fds();
     const bool want_fabric = opt.handle_type == HandleChoice::kFabric ||
-                             (opt.handle_type == HandleChoice::kAuto && !opt.posix_fd_supported && opt.fabric_supported);
+                             (opt.handle_type == HandleChoice::kAuto && !fds_usable && opt.fabric_supported);
     if (want_fabric) {
       if (!opt.fabric_supported) {
         throw std::runtime_error("fabric handles were requested but this GPU does not support them");
@@ -102,6 +105,12 @@ void SymmetricMemory::build(Bootstrap& comm, const SymmOptions& opt) {
     } else {
       if (!opt.posix_fd_supported) {
         throw std::runtime_error("POSIX file-descriptor handles are not supported by this GPU");
+      }
+      if (!comm.can_pass_fds()) {
+        throw std::runtime_error(
+            "the control plane runs over TCP and cannot pass file descriptors; sharing memory between hosts needs "
+            "fabric handles (IMEX), which this GPU does not report" +
+            std::string(opt.handle_type == HandleChoice::kPosixFd ? " (and --handle-type posix_fd was requested)" : ""));
       }
       handle_type = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
       handle_kind = "posix_fd";

@@ -51,6 +51,8 @@ _SIGNATURES = {
     "msharp_init_latency_csv_header": (c_char_p, []),
     "msharp_run_cpu_only": (c_char_p, [c_int, POINTER(c_char_p)]),
     "msharp_bootstrap_connect": (c_void_p, [c_int, c_int, c_char_p, c_int]),
+    "msharp_bootstrap_connect_address": (c_void_p, [c_int, c_int, c_char_p, c_char_p, c_int]),
+    "msharp_bootstrap_can_pass_fds": (c_int, [c_void_p]),
     "msharp_bootstrap_destroy": (None, [c_void_p]),
     "msharp_bootstrap_barrier": (c_int, [c_void_p]),
     "msharp_bootstrap_allgather": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),

@@ -1,8 +1,10 @@
-"""Control plane between the rank processes of one host (Unix-socket hub in the native library).
+"""Control plane between the rank processes (socket hub in the native library): Unix-domain
+sockets on one host, TCP to rank 0 when an address is given (jobs that span hosts).
 
 It does what MPI does for the reference project (handle exchange, barriers, small reductions;
 call sites listed in the reference at src/fabric_memory.cc:111-169 and src/main.cc:91-195) and
-can pass file descriptors between processes, which the POSIX-FD memory handles need.
+can pass file descriptors between processes of one host, which the POSIX-FD memory handles need
+(over TCP `can_pass_fds` is false and symmetric memory uses fabric handles).
 Every call is collective, has a deadline, and raises `NativeError` naming the rank that failed.
 """
 from __future__ import annotations
@@ -16,20 +18,43 @@ from .. import _native as N
 
 
 class Bootstrap:
-    def __init__(self, rank: int, world: int, session: str = "default", timeout_ms: int = 30000):
+    def __init__(self, rank: int, world: int, session: str = "default", timeout_ms: int = 30000,
+                 address: str | None = None):
         self.rank = rank
         self.world = world
         self.session = session
-        self._h = N.pointer(N.lib.msharp_bootstrap_connect(rank, world, session.encode(), timeout_ms))
+        self.address = address or ""
+        self._h = N.pointer(N.lib.msharp_bootstrap_connect_address(rank, world, session.encode(),
+                                                                   self.address.encode(), timeout_ms))
 
     @classmethod
     def from_env(cls, timeout_ms: int = 60000) -> "Bootstrap":
         """RANK / WORLD_SIZE as set by torchrun or by this package's launcher; the session name
-        comes from MSHARP_SESSION, else from MASTER_PORT."""
+        comes from MSHARP_SESSION, else from MASTER_PORT. MSHARP_HUB_ADDR=host:port selects TCP
+        (rank 0 listens on that port; needed only when the ranks are on more than one host)."""
         rank = int(os.environ.get("RANK", "0"))
         world = int(os.environ.get("WORLD_SIZE", "1"))
         session = os.environ.get("MSHARP_SESSION") or ("port" + os.environ.get("MASTER_PORT", "0"))
-        return cls(rank, world, session, timeout_ms)
+        return cls(rank, world, session, timeout_ms, os.environ.get("MSHARP_HUB_ADDR"))
+
+    @classmethod
+    def from_process_group(cls, group=None, timeout_ms: int = 60000, address: str | None = None) -> "Bootstrap":
+        """Join through an initialised `torch.distributed` process group (any backend; gloo on CPU
+        hosts): rank 0 of the group picks a fresh session name and broadcasts it, so nothing has
+        to be agreed out of band. `address` as in the constructor."""
+        import uuid
+
+        import torch.distributed as dist
+
+        rank = dist.get_rank(group)
+        world = dist.get_world_size(group)
+        box = [uuid.uuid4().hex[:16] if rank == 0 else None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls(rank, world, "pg" + box[0], timeout_ms, address)
+
+    @property
+    def can_pass_fds(self) -> bool:
+        return bool(N.lib.msharp_bootstrap_can_pass_fds(self._h))
 
     @property
     def handle(self) -> int:

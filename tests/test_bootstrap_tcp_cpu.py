@@ -1,0 +1,206 @@
+"""The control plane over TCP and fabric-handle sharing, among CPU processes (no GPU).
+
+This is the configuration of a job that spans hosts: ranks reach rank 0 over TCP, descriptors
+cannot be passed, so symmetric memory is shared through fabric handles. The fake driver stands
+in for the GPUs and for IMEX: its fabric handle is the name of a shared-memory object that any
+process of this machine can open. All ranks run on this machine and use 127.0.0.1.
+"""
+import multiprocessing as mp
+import os
+import socket
+import struct
+import time
+
+import numpy as np
+import pytest
+
+CTX = mp.get_context("spawn")
+FABRIC_SUPPORTED = 128  # CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def run_ranks(target, world, *args, timeout=60):
+    session = f"tcp{os.getpid()}_{time.monotonic_ns()}"
+    address = f"127.0.0.1:{free_port()}"
+    q = CTX.Queue()
+    procs = [CTX.Process(target=target, args=(r, world, session, address, q) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    deadline = time.time() + timeout
+    while len(results) < world and time.time() < deadline:
+        try:
+            rank, value = q.get(timeout=0.5)
+            results[rank] = value
+        except Exception:
+            if all(not p.is_alive() for p in procs) and q.empty():
+                break
+    for p in procs:
+        p.join(timeout=10)
+        if p.is_alive():
+            p.kill()
+    return results
+
+
+def _collectives(rank, world, session, address, q):
+    from mnnvl_sharp_b200.parallel import Bootstrap
+
+    try:
+        with Bootstrap(rank, world, session, timeout_ms=20000, address=address) as b:
+            b.barrier()
+            gathered = b.allgather_bytes(bytes([rank]) * 64)  # the size of a fabric handle
+            root_value = b.broadcast_bytes(b"R%d" % rank, root=world - 1)
+            mx = b.reduce_max(float(rank))
+            fd_error = ""
+            try:
+                b.allgather_fd(0)
+            except Exception as ex:  # noqa: BLE001
+                fd_error = str(ex)
+            q.put((rank, dict(gathered=[g[0] for g in gathered], root=root_value, mx=mx, can=b.can_pass_fds, fd_error=fd_error)))
+    except Exception as ex:  # noqa: BLE001
+        q.put((rank, repr(ex)))
+
+
+@pytest.mark.parametrize("world", [2, 5])
+def test_collectives_over_tcp(world):
+    res = run_ranks(_collectives, world)
+    assert sorted(res) == list(range(world)), res
+    for r in res.values():
+        assert isinstance(r, dict), r
+        assert r["gathered"] == list(range(world)) and r["root"] == b"R%d" % (world - 1) and r["mx"] == world - 1
+        assert r["can"] is False and "cannot be passed over TCP" in r["fd_error"]
+
+
+def _other_session(rank, world, session, address, q):
+    from mnnvl_sharp_b200._native import NativeError
+    from mnnvl_sharp_b200.parallel import Bootstrap
+
+    # rank 1 was given the port of another job by mistake: the hub turns it away and reports it missing
+    mine = session if rank == 0 else session + "_other"
+    try:
+        with Bootstrap(rank, world, mine, timeout_ms=1500, address=address) as b:
+            b.barrier()
+        q.put((rank, "joined"))
+    except NativeError as ex:
+        q.put((rank, str(ex)))
+
+
+def test_a_rank_of_another_session_is_turned_away():
+    res = run_ranks(_other_session, 2)
+    assert "timed out waiting for rank(s) 1" in res[0], res
+    assert res[1] != "joined" and ("lost the connection" in res[1] or "timed out" in res[1]), res
+
+
+def _stranger(rank, world, session, address, q):
+    from mnnvl_sharp_b200.parallel import Bootstrap
+
+    if rank == 1:
+        time.sleep(0.3)
+        host, port = address.rsplit(":", 1)
+        s = socket.create_connection((host, int(port)))
+        s.sendall(struct.pack("<IIIiQ", 0x4D534850, 1, 0, 1, 2))  # right magic and rank, wrong session tag
+        time.sleep(0.2)
+        s.close()
+    with Bootstrap(rank, world, session, timeout_ms=8000, address=address) as b:
+        b.barrier()
+        q.put((rank, "ok"))
+
+
+def test_hub_drops_a_stranger_and_still_accepts_the_rank():
+    assert run_ranks(_stranger, 2) == {0: "ok", 1: "ok"}
+
+
+def test_a_bad_address_is_refused_with_a_message():
+    from mnnvl_sharp_b200._native import NativeError
+    from mnnvl_sharp_b200.parallel import Bootstrap
+
+    for bad in ("nohost", "host:", "host:notaport", "host:70000"):
+        with pytest.raises(NativeError, match="address|port"):
+            Bootstrap(1, 2, "s", timeout_ms=200, address=bad)
+
+
+def _symm(rank, world, session, address, q, fabric, handle_type):
+    from mnnvl_sharp_b200 import _native as N
+    from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+
+    N.lib.msharp_fake_driver_reset(8)
+    N.lib.msharp_fake_driver_set_attribute(FABRIC_SUPPORTED, 1 if fabric else 0)
+    out = {}
+    try:
+        with Bootstrap(rank, world, session, timeout_ms=20000, address=address) as b:
+            try:
+                comm = Communicator(b, rank % 8, fake_driver=True, handle_type=handle_type)
+                buf = comm.alloc(3 << 20, layout="single")
+                out["symm"] = buf.info
+                buf.canary_check()
+                buf.write(np.full(64, 50 + rank, dtype=np.uint8), offset=8192)
+                b.barrier()
+                out["peer_bytes"] = [int(buf.read(1, offset=8192, slot_rank=r)[0]) for r in range(world)]
+                b.barrier()
+                buf.free()
+                comm.close()
+            except Exception as ex:  # noqa: BLE001
+                out["alloc_error"] = str(ex)
+            leaks = (N.ctypes.c_int * 4)()
+            N.lib.msharp_fake_driver_leaks(leaks)
+            out["leaks"] = list(leaks)
+    except Exception as ex:  # noqa: BLE001
+        out["error"] = repr(ex)
+    q.put((rank, out))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_symmetric_memory_over_tcp_uses_fabric_handles(world):
+    before = set(n for n in os.listdir("/dev/shm") if n.startswith("msharp-fake-"))
+    res = run_ranks(_symm, world, True, "auto")
+    assert sorted(res) == list(range(world)), res
+    for r in res.values():
+        assert "error" not in r and "alloc_error" not in r, r
+        assert r["symm"]["handle_type"] == "fabric" and r["symm"]["multicast_bound"] is True
+        assert r["peer_bytes"] == [50 + k for k in range(world)]
+        assert r["leaks"] == [0, 0, 0, 0]
+    after = set(n for n in os.listdir("/dev/shm") if n.startswith("msharp-fake-"))
+    assert after <= before  # every named object was unlinked by its owner
+
+
+@pytest.mark.parametrize("handle_type", ["auto", "posix_fd"])
+def test_tcp_without_fabric_support_fails_on_all_ranks_with_the_reason(handle_type):
+    res = run_ranks(_symm, 2, False, handle_type)
+    for r in res.values():
+        assert "error" not in r, r
+        assert "fabric handles" in r["alloc_error"], r
+        assert r["leaks"] == [0, 0, 0, 0]
+
+
+def _pg(rank, world, port, q):
+    import torch.distributed as dist
+
+    from mnnvl_sharp_b200.parallel import Bootstrap
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        with Bootstrap.from_process_group() as b:
+            vals = b.allgather_float(rank + 0.5)
+            q.put((rank, (b.session, vals, b.can_pass_fds)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bootstrap_from_a_torch_distributed_group():
+    world = 3
+    port = free_port()
+    q = CTX.Queue()
+    procs = [CTX.Process(target=_pg, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    sessions = {v[0] for v in res.values()}
+    assert len(sessions) == 1 and next(iter(sessions)).startswith("pg")
+    assert all(v[1] == [0.5, 1.5, 2.5] and v[2] is True for v in res.values())

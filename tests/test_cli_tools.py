@@ -2,6 +2,7 @@
 replaced by a stub process where one would be started)."""
 import csv
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -89,8 +90,15 @@ def test_launcher_scans_flags_and_writes_artefacts(tmp_path, capsys):
     rack_path = tmp_path / "rack.yaml"
     rack_path.write_text(RACK)
     emit = tmp_path / "emit"
-    rc = run.main([str(rack_path), "--rank-count", "3", "--emit-dir", str(emit), "--json"])
-    assert rc == 3  # two remote trays: artefacts only
+    rc = run.main([str(rack_path), "--rank-count", "3", "--emit-dir", str(emit), "--json", "--dry-run"])
+    assert rc == 0  # two remote trays: artefacts and the per-host commands, nothing started
+    shown = capsys.readouterr().out
+    assert "hub=10.0.0.11:29431" in shown
+    assert shown.count("_build --no-torch") == 2 and "tray-b:" in shown  # remote build + inventory copy per host
+    starts = [line for line in shown.splitlines() if line.startswith("+ ssh") and "mnnvl_sharp_allreduce" in line]
+    assert len(starts) == 2 and all("MSHARP_HUB_ADDR=10.0.0.11:29431" in line for line in starts)
+    assert "MNNVL_HOST_LABEL=tray-a" in starts[0] and "MNNVL_HOST_LABEL=tray-b" in starts[1]
+    assert all("--rank-count 3" in line and "--json" in line and "--dry-run" not in line for line in starts)
     assert (emit / "hosts.txt").read_text() == "tray-a:2,tray-b:1"
     assert (emit / "rankfile").read_text().splitlines()[1] == "rank 1=tray-b slot=0"
     assert "Port 2222" in (emit / "ssh_config").read_text()
@@ -98,6 +106,68 @@ def test_launcher_scans_flags_and_writes_artefacts(tmp_path, capsys):
     assert (emit / "selected_entries.tsv").read_text().splitlines()[1] == "tray-b\t10.0.0.12\t2222"
     with pytest.raises(SystemExit):
         run.main([str(rack_path), "--rank-count", "9"])
+
+
+def test_multi_host_launch_end_to_end_without_gpus(tmp_path, monkeypatch, capfd):
+    """Two trays on "different hosts": the launcher prepares and starts each host through its ssh
+    command (here a script that runs the command on this machine), every host's copy of the binary
+    starts its own ranks, they meet over TCP, share memory through fabric handles (the driver
+    stand-in), pass the canary test of every slot, and rank 0 prints the report."""
+    import json
+    import socket
+    import stat
+
+    from mnnvl_sharp_b200 import _build
+
+    _build.build_native()
+    rack_path = tmp_path / "rack.yaml"
+    rack_path.write_text("rack:\n  - hostA:\n      - hostname: 127.0.0.1\n      - device: [0, 1]\n"
+                         "  - hostB:\n      - hostname: 127.0.0.1\n      - device: [2, 3, 4]\n")
+    fake_ssh = tmp_path / "fake_ssh"
+    fake_ssh.write_text("#!/bin/sh\n# usage: fake_ssh -F config host command\nshift 3\nexec sh -c \"$1\"\n")
+    fake_scp = tmp_path / "fake_scp"
+    fake_scp.write_text("#!/bin/sh\n# usage: fake_scp -F config source host:destination\nexec cp \"$3\" \"${4#*:}\"\n")
+    for f in (fake_ssh, fake_scp):
+        f.chmod(f.stat().st_mode | stat.S_IEXEC)
+    app_dir = tmp_path / "app"
+    (app_dir / "mnnvl_sharp_b200" / "_C").mkdir(parents=True)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    monkeypatch.setenv("MNNVL_SSH_COMMAND", str(fake_ssh))
+    monkeypatch.setenv("MNNVL_SCP_COMMAND", str(fake_scp))
+    monkeypatch.setenv("MNNVL_SKIP_REMOTE_BUILD", "1")
+    monkeypatch.setenv("MNNVL_APP_DIR", str(app_dir))
+    monkeypatch.setenv("MNNVL_LOCAL_LABEL", "hostA")
+    monkeypatch.setenv("MSHARP_HUB_PORT", str(port))
+    monkeypatch.setenv("MSHARP_DRIVER", "fake")
+    monkeypatch.setenv("MSHARP_FAKE_FABRIC", "1")
+    monkeypatch.setenv("MSHARP_BOOTSTRAP_TIMEOUT_MS", "20000")
+    rc = run.main([str(rack_path), "--rank-count", "4", "--init-only", "--json", "--no-pin", "--bytes", "4194304",
+                   "--reference-check-bytes", "4096"])
+    out = capfd.readouterr().out
+    assert rc == 0, out
+    assert (app_dir / "mnnvl_sharp_b200" / "_C" / "mnnvl_sharp_allreduce").exists() and (app_dir / ".launch_rack.yaml").exists()
+    report = json.loads([line for line in out.splitlines() if line.startswith("{")][-1])
+    assert report["selected_rank_count"] == 4 and report["handle_type"] == "fabric" and report["init_only"] is True
+    assert [(m["rank"], m["host_label"], m["local_rank"], m["gpu"]) for m in report["host_mapping"]] == [
+        (0, "hostA", 0, 0), (1, "hostB", 0, 2), (2, "hostA", 1, 1), (3, "hostB", 1, 3)]
+    assert len(report["peer_init_local_ms_by_rank"]) == 4
+
+
+def test_multi_host_launch_reports_a_host_that_has_no_ranks(tmp_path, monkeypatch):
+    import subprocess
+
+    from mnnvl_sharp_b200 import _build
+
+    exe = _build.build_native()["exe"]
+    rack_path = tmp_path / "rack.yaml"
+    rack_path.write_text("rack:\n  - hostA:\n      - hostname: 127.0.0.1\n      - device: [0]\n"
+                         "  - hostB:\n      - hostname: 127.0.0.1\n      - device: [0]\n")
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE")}
+    env["MNNVL_HOST_LABEL"] = "elsewhere"
+    done = subprocess.run([str(exe), "--rack-config", str(rack_path), "--init-only"], env=env, capture_output=True, text=True)
+    assert done.returncode == 1 and "none of its ranks is on this host ('elsewhere')" in done.stderr
 
 
 def test_preflight_helpers(tmp_path):
