@@ -1,7 +1,14 @@
 // Native unit tests of the host-side library (no GPU): run `msharp_cpp_tests`; exit code 0 = pass.
 // They cover what is easier to state in C++ than through the C interface: the JSON / human
 // report writers (key order of the reference project's src/main.cc:295-354), the CSV row,
-// align_up overflow handling, topology validation messages, and the device-status texts.
+// align_up overflow handling, topology validation messages, and the device-status texts; and the
+// multi-host configuration (TCP control plane + fabric handles) with the ranks as threads, so that
+// the address and undefined-behaviour sanitizers see that code too.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -10,9 +17,12 @@
 #include <limits>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <vector>
 
+#include "msharp/bootstrap.h"
 #include "msharp/comm_context.h"
+#include "msharp/fake_driver.h"
 #include "msharp/config.h"
 #include "msharp/json.h"
 #include "msharp/numerics.h"
@@ -229,6 +239,114 @@ void test_codec_spot_checks() {
   EXPECT(reference_f16_bits(0, 0) == 0x0000);  // mix = 7 -> table entry 7
 }
 
+int free_tcp_port() {
+  const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+  sockaddr_in addr;
+  std::memset(&addr, 0, sizeof(addr));
+  addr.sin_family = AF_INET;
+  addr.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  socklen_t len = sizeof(addr);
+  int port = 0;
+  if (fd >= 0 && ::bind(fd, reinterpret_cast<sockaddr*>(&addr), sizeof(addr)) == 0 &&
+      ::getsockname(fd, reinterpret_cast<sockaddr*>(&addr), &len) == 0) {
+    port = ntohs(addr.sin_port);
+  }
+  if (fd >= 0) {
+    ::close(fd);
+  }
+  return port;
+}
+
+void test_tcp_control_plane_and_fabric_handles() {
+  using namespace msharp;
+  const int world = 3;
+  const int port = free_tcp_port();
+  EXPECT(port > 0);
+  fake_driver_reset(8);
+  fake_driver_set_attribute(CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED, 1);
+  std::vector<std::string> errors(world);
+  std::vector<std::string> kinds(world);
+  std::vector<int> seen_ok(world, 0);
+  std::vector<std::thread> threads;
+  for (int rank = 0; rank < world; ++rank) {
+    threads.emplace_back([&, rank] {
+      try {
+        BootstrapOptions opt;
+        opt.rank = rank;
+        opt.world = world;
+        opt.session = "cpp-tcp";
+        opt.address = "127.0.0.1:" + std::to_string(port);
+        opt.timeout_ms = 20000;
+        std::unique_ptr<Bootstrap> comm = Bootstrap::connect(opt);
+        if (comm->can_pass_fds()) {
+          throw std::runtime_error("a TCP control plane claims that it can pass descriptors");
+        }
+        bool refused = false;
+        try {
+          comm->allgather_fd(-1);
+        } catch (const BootstrapError&) {
+          refused = true;
+        }
+        if (!refused) {
+          throw std::runtime_error("allgather_fd over TCP did not throw");
+        }
+        const std::vector<uint64_t> all = comm->allgather_u64(100u + static_cast<uint64_t>(rank));
+        for (int r = 0; r < world; ++r) {
+          if (all[static_cast<std::size_t>(r)] != 100u + static_cast<uint64_t>(r)) {
+            throw std::runtime_error("allgather over TCP returned the wrong values");
+          }
+        }
+        SymmOptions so;
+        so.payload_bytes = 1 << 20;
+        so.device_ordinal = rank;
+        so.cu_device = rank;
+        so.posix_fd_supported = true;
+        so.fabric_supported = true;
+        so.multicast_supported = true;
+        so.want_multicast = true;
+        std::unique_ptr<SymmetricMemory> mem = SymmetricMemory::create(fake_driver(), *comm, so);
+        kinds[static_cast<std::size_t>(rank)] = mem->handle_kind;
+        const uint32_t mine = 0xabc00000u + static_cast<uint32_t>(rank);
+        mem->copy_from_host(rank, 64, &mine, sizeof(mine));
+        comm->barrier();
+        int ok = 1;
+        for (int r = 0; r < world; ++r) {
+          uint32_t got = 0;
+          mem->copy_to_host(&got, r, 64, sizeof(got));
+          ok = ok && got == 0xabc00000u + static_cast<uint32_t>(r);
+        }
+        seen_ok[static_cast<std::size_t>(rank)] = ok;
+        comm->barrier();
+        mem->destroy();
+      } catch (const std::exception& ex) {
+        errors[static_cast<std::size_t>(rank)] = ex.what();
+      }
+    });
+  }
+  for (std::thread& t : threads) {
+    t.join();
+  }
+  for (int rank = 0; rank < world; ++rank) {
+    if (!errors[static_cast<std::size_t>(rank)].empty()) {
+      std::printf("rank %d: %s\n", rank, errors[static_cast<std::size_t>(rank)].c_str());
+    }
+    EXPECT(errors[static_cast<std::size_t>(rank)].empty());
+    EXPECT(kinds[static_cast<std::size_t>(rank)] == "fabric");
+    EXPECT(seen_ok[static_cast<std::size_t>(rank)] == 1);
+  }
+  const FakeDriverLeaks leaks = fake_driver_leaks();
+  EXPECT(leaks.handles == 0 && leaks.reservations == 0 && leaks.mappings == 0 && leaks.multicast_bindings == 0);
+  EXPECT(throws_with([] {
+    BootstrapOptions bad;
+    bad.rank = 1;
+    bad.world = 2;
+    bad.address = "no-port-here";
+    bad.timeout_ms = 100;
+    Bootstrap::connect(bad);
+  }, "host:port"));
+  fake_driver_reset(8);
+}
+
 }  // namespace
 
 int main() {
@@ -239,6 +357,7 @@ int main() {
   test_topology_validation();
   test_status_text();
   test_codec_spot_checks();
+  test_tcp_control_plane_and_fabric_handles();
   if (g_failures == 0) {
     std::printf("all native tests passed\n");
     return 0;

@@ -130,7 +130,11 @@ def prepare_remote(label: str, rack_path: str, ssh_config: Path, app_dir: str, d
     if not dry_run:
         for step in steps:
             print("+ " + " ".join(shlex.quote(s) for s in step), flush=True)
-            rc = subprocess.call(step)
+            try:
+                rc = subprocess.call(step)
+            except FileNotFoundError:
+                raise SystemExit(f"error: '{step[0]}' is not installed; it is needed to reach {label} "
+                                 "(MNNVL_SSH_COMMAND / MNNVL_SCP_COMMAND name other programs)") from None
             if rc != 0:
                 raise SystemExit(f"error: preparing {label} failed (exit {rc}): {' '.join(step)}")
     return steps
@@ -199,12 +203,13 @@ def main(argv: list[str] | None = None) -> int:
     if not count_arg:
         flags += ["--rank-count", str(rank_count)]
 
-    if len(labels) == 1 and is_local(labels[0]):
+    if "--cpu-only" in flags or (len(labels) == 1 and is_local(labels[0])):
+        # the host-only oracle needs no GPU and no other host: it always runs here
         exe = _build.build_native()["exe"] if not dry_run else REPO_ROOT / BINARY_REL
         cmd = [str(exe), "--rack-config", str(rack_yaml.resolve())] + flags
         print(f"launching mnnvl_sharp_allreduce rank_count={rank_count} selection={selection} hosts={texts['hosts']}", flush=True)
         env = dict(os.environ)
-        if labels[0].split(".")[0] != "localhost":
+        if len(labels) == 1 and labels[0].split(".")[0] != "localhost":
             env.setdefault("MNNVL_HOST_LABEL", labels[0])
         if dry_run:
             print(" ".join(shlex.quote(c) for c in cmd))
