@@ -107,6 +107,21 @@ def busbw(nbytes: int, ms: float, n: int) -> float:
     return alg if n == 1 else alg * 2.0 * (n - 1) / n
 
 
+LINK_GB_S = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
+
+
+def roofline(nbytes: int, ms: float, n: int) -> dict:
+    """Bound of the in-switch all-reduce: every GPU sends its buffer once into the switch (the
+    reduce of the other ranks' slices) plus its reduced 1/N slice, and receives the same amount,
+    so t >= S (1 + 1/N) / link. In bus-bandwidth terms that is link * 2 (N-1) / (N+1)."""
+    if n == 1:
+        return {"note": "one rank moves nothing over NVLink; no link bound applies"}
+    bound_ms = nbytes * (1.0 + 1.0 / n) / (LINK_GB_S * 1e6)
+    return {"link_gb_s_measured": LINK_GB_S, "bound_ms": round(bound_ms, 4),
+            "bound_busbw_gb_s": round(LINK_GB_S * 2.0 * (n - 1) / (n + 1), 1),
+            "fraction_of_measured": round(bound_ms / ms, 3)}
+
+
 def run_ours(args) -> int:
     import numpy as np
     import torch
@@ -243,6 +258,9 @@ def run_ours(args) -> int:
             "aggregate_logical_gb_s": round(world * nbytes / (ms * 1e6), 3),
             "f16": {"ms_per_step": round(results["f16"], 6), "busbw_gb_s": round(busbw(nbytes, results["f16"], world), 3),
                     "algbw_gb_s": round(nbytes / (results["f16"] * 1e6), 3)},
+            "roofline": roofline(nbytes, ms, world),
+            "scaling_note": "bus bandwidth is normalised per GPU (ideal: flat in N, at the link bound); the whole-job "
+                            "figure is aggregate_logical_gb_s = N * bytes / time",
             "checks": checks,
             "clocks": clocks,
             "e2e": {"value": round(busbw(nbytes, e2e_ms, world), 3), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4),
