@@ -15,8 +15,6 @@ import torch
 from .. import _native as N
 from ..parallel.symmetric import Communicator, SymmetricBuffer
 
-_NATIVE_STREAM_OK = True
-
 
 def _stream() -> int:
     return int(torch.cuda.current_stream().cuda_stream)
