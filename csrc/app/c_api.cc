@@ -378,6 +378,7 @@ void* msharp_comm_create(void* bootstrap, int device_ordinal, int wait_timeout_m
     base.cu_device = handle->rank.cu_device;
     base.posix_fd_supported = handle->caps.posix_fd_handle_supported;
     base.fabric_supported = handle->caps.fabric_handle_supported;
+    base.fabric_unusable_reason = handle->caps.fabric_probe_error;
     base.multicast_supported = handle->caps.multicast_supported;
     if (!handle->bootstrap->all_true(handle->caps.vmm_supported)) {
       throw std::runtime_error("one or more GPUs lack virtual memory management support");
@@ -420,6 +421,7 @@ const char* msharp_comm_info(void* comm) {
     w.key("vmm").value(h->caps.vmm_supported);
     w.key("posix_fd").value(h->caps.posix_fd_handle_supported);
     w.key("fabric").value(h->caps.fabric_handle_supported);
+    w.key("fabric_probe_error").value(h->caps.fabric_probe_error);
     w.key("multicast").value(h->caps.multicast_supported);
     w.key("bulk_multimem").value(h->caps.bulk_multimem_supported);
     w.key("control_multicast").value(h->ctx->has_multicast());

@@ -253,6 +253,7 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   base.cu_device = run.rank.cu_device;
   base.posix_fd_supported = run.caps.posix_fd_handle_supported;
   base.fabric_supported = run.caps.fabric_handle_supported;
+  base.fabric_unusable_reason = run.caps.fabric_probe_error;
   base.multicast_supported = run.caps.multicast_supported;
 
   RunReport report;

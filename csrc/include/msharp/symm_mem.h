@@ -38,6 +38,7 @@ struct SymmOptions {
   CUdevice cu_device = 0;
   bool posix_fd_supported = true;
   bool fabric_supported = false;
+  std::string fabric_unusable_reason;  // from the capability probe; quoted when fabric handles are needed
   bool multicast_supported = true;
 };
 

@@ -40,7 +40,8 @@ struct RankInfo {
 struct CapabilityInfo {
   bool vmm_supported = false;
   bool posix_fd_handle_supported = false;
-  bool fabric_handle_supported = false;
+  bool fabric_handle_supported = false;  // the attribute says yes AND a trial allocation + export worked
+  std::string fabric_probe_error;        // why not, when the attribute says yes but the trial failed
   bool multicast_supported = false;
   bool sharp_e4m3_supported = false;       // "e4m3_legacy" in reports
   bool sharp_tma_async_supported = false;  // "f16_tma_async" in reports

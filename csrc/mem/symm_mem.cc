@@ -98,7 +98,9 @@ void SymmetricMemory::build(Bootstrap& comm, const SymmOptions& opt) {
                              (opt.handle_type == HandleChoice::kAuto && !fds_usable && opt.fabric_supported);
     if (want_fabric) {
       if (!opt.fabric_supported) {
-        throw std::runtime_error("fabric handles were requested but this GPU does not support them");
+        throw std::runtime_error("fabric handles were requested but cannot be used here" +
+                                 (opt.fabric_unusable_reason.empty() ? std::string(": the GPU does not report them")
+                                                                     : ": " + opt.fabric_unusable_reason));
       }
       handle_type = CU_MEM_HANDLE_TYPE_FABRIC;
       handle_kind = "fabric";
@@ -109,8 +111,11 @@ void SymmetricMemory::build(Bootstrap& comm, const SymmOptions& opt) {
       if (!comm.can_pass_fds()) {
         throw std::runtime_error(
             "the control plane runs over TCP and cannot pass file descriptors; sharing memory between hosts needs "
-            "fabric handles (IMEX), which this GPU does not report" +
-            std::string(opt.handle_type == HandleChoice::kPosixFd ? " (and --handle-type posix_fd was requested)" : ""));
+            "fabric handles" +
+            std::string(opt.handle_type == HandleChoice::kPosixFd
+                            ? ", but --handle-type posix_fd was requested"
+                            : (opt.fabric_unusable_reason.empty() ? ", which this GPU does not report"
+                                                                  : ", which cannot be used here: " + opt.fabric_unusable_reason)));
       }
       handle_type = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
       handle_kind = "posix_fd";

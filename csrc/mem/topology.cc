@@ -106,6 +106,35 @@ bool probe_bulk_multimem(const DriverApi& api, std::string* detail) {
   return false;
 }
 
+// The attribute only says that the GPU and driver know fabric handles. Whether this process may
+// use them also depends on the IMEX channel of its container, which shows only when an allocation
+// that asks for such a handle is created: do that once, with one granule, and give it back.
+bool probe_fabric_handles(const DriverApi& api, int device_ordinal, std::string* why) {
+  CUmemAllocationProp prop;
+  std::memset(&prop, 0, sizeof(prop));
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device_ordinal;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_FABRIC;
+  std::size_t granularity = 0;
+  CUresult rc = api.MemGetAllocationGranularity(&granularity, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM);
+  CUmemGenericAllocationHandle handle = 0;
+  if (rc == CUDA_SUCCESS) {
+    rc = api.MemCreate(&handle, granularity, &prop, 0);
+  }
+  if (rc == CUDA_SUCCESS) {
+    CUmemFabricHandle blob;
+    rc = api.MemExportToShareableHandle(&blob, handle, CU_MEM_HANDLE_TYPE_FABRIC, 0);
+    api.MemRelease(handle);
+  }
+  if (rc != CUDA_SUCCESS && why != nullptr) {
+    *why = driver_error_text(api, rc) +
+           " (fabric handles need the IMEX service and an IMEX channel, /dev/nvidia-caps-imex-channels/channel0, "
+           "visible in this container)";
+  }
+  return rc == CUDA_SUCCESS;
+}
+
 CapabilityInfo query_capabilities(const DriverApi& api, RankInfo* rank) {
   if (rank == nullptr) {
     throw std::runtime_error("query_capabilities received null RankInfo");
@@ -123,6 +152,9 @@ CapabilityInfo query_capabilities(const DriverApi& api, RankInfo* rank) {
   caps.vmm_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_VIRTUAL_MEMORY_MANAGEMENT_SUPPORTED) != 0;
   caps.posix_fd_handle_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED) != 0;
   caps.fabric_handle_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED) != 0;
+  if (caps.fabric_handle_supported && !probe_fabric_handles(api, rank->gpu_ordinal, &caps.fabric_probe_error)) {
+    caps.fabric_handle_supported = false;
+  }
   caps.multicast_supported = attribute(api, dev, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED) != 0;
   rank->host_numa_id = attribute(api, dev, CU_DEVICE_ATTRIBUTE_HOST_NUMA_ID);
   // The FP8 multimem forms are compiled in unconditionally (sm_100a only build).

@@ -124,12 +124,15 @@ def test_a_bad_address_is_refused_with_a_message():
             Bootstrap(1, 2, "s", timeout_ms=200, address=bad)
 
 
-def _symm(rank, world, session, address, q, fabric, handle_type):
+def _symm(rank, world, session, address, q, fabric, handle_type, probe_fails=False):
     from mnnvl_sharp_b200 import _native as N
     from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
 
     N.lib.msharp_fake_driver_reset(8)
     N.lib.msharp_fake_driver_set_attribute(FABRIC_SUPPORTED, 1 if fabric else 0)
+    if probe_fails:
+        # what a container without an IMEX channel shows: the attribute says yes, the allocation says no
+        N.lib.msharp_fake_driver_fail_call(b"cuMemCreate", 1, 800)  # CUDA_ERROR_NOT_PERMITTED
     out = {}
     try:
         with Bootstrap(rank, world, session, timeout_ms=20000, address=address) as b:
@@ -174,6 +177,14 @@ def test_tcp_without_fabric_support_fails_on_all_ranks_with_the_reason(handle_ty
     for r in res.values():
         assert "error" not in r, r
         assert "fabric handles" in r["alloc_error"], r
+        assert r["leaks"] == [0, 0, 0, 0]
+
+
+def test_fabric_attribute_without_a_usable_channel_is_found_by_the_probe_and_explained():
+    res = run_ranks(_symm, 2, True, "auto", True)
+    for r in res.values():
+        assert "error" not in r, r
+        assert "CUDA_ERROR_NOT_PERMITTED" in r["alloc_error"] and "IMEX" in r["alloc_error"], r
         assert r["leaks"] == [0, 0, 0, 0]
 
 
