@@ -293,6 +293,24 @@ void* msharp_bootstrap_connect_address(int rank, int world, const char* session,
 
 void msharp_bootstrap_destroy(void* b) { delete static_cast<msharp::Bootstrap*>(b); }
 
+const char* msharp_bootstrap_env_options(void) {
+  return guarded_text([&] {
+    const msharp::BootstrapOptions opt = msharp::Bootstrap::options_from_env();
+    std::string source;
+    const bool found = msharp::Bootstrap::rank_from_env(nullptr, nullptr, &source);
+    msharp::JsonWriter w;
+    w.begin_object();
+    w.key("rank").value(opt.rank);
+    w.key("world").value(opt.world);
+    w.key("session").value(opt.session);
+    w.key("address").value(opt.address);
+    w.key("timeout_ms").value(opt.timeout_ms);
+    w.key("launched_by").value(found ? source : std::string("nothing (single process)"));
+    w.end_object();
+    return w.str();
+  });
+}
+
 int msharp_bootstrap_can_pass_fds(void* b) { return static_cast<msharp::Bootstrap*>(b)->can_pass_fds() ? 1 : 0; }
 
 int msharp_bootstrap_barrier(void* b) {

@@ -8,9 +8,10 @@
 // ranks whose tray label is this host's (MNNVL_HOST_LABEL, else the short host name), and all
 // ranks meet at rank 0's TCP control socket (--hub-address / MSHARP_HUB_ADDR, default: the
 // control hostname of rank 0's tray, port MSHARP_HUB_PORT or 29431).
-// Started with them (by its own launcher, by torchrun, or by any other process manager) it is
-// one rank. Exit codes as in the reference's main (src/main.cc:491-505): 0 ok, 2 result check
-// failed, 1 error; errors are printed as "rank R error: ...".
+// Started with them (by its own launcher, by torchrun, or under mpirun / srun, whose rank variables
+// are understood too; no MPI library is linked) it is one rank. Exit codes as in the reference's
+// main (src/main.cc:491-505): 0 ok, 2 result check failed, 1 error; errors are printed as
+// "rank R error: ...".
 #include <unistd.h>
 
 #include <cstdlib>
@@ -30,11 +31,7 @@
 
 namespace {
 
-bool launched_as_rank() {
-  const char* rank = std::getenv("RANK");
-  const char* world = std::getenv("WORLD_SIZE");
-  return rank != nullptr && *rank != '\0' && world != nullptr && *world != '\0';
-}
+bool launched_as_rank() { return msharp::Bootstrap::rank_from_env(nullptr, nullptr, nullptr); }
 
 std::string self_path(const char* argv0) {
   char buf[4096];
@@ -77,9 +74,7 @@ const msharp::DriverApi& chosen_driver() {
 
 int main(int argc, char** argv) {
   int rank = 0;
-  if (const char* r = std::getenv("RANK"); r != nullptr) {
-    rank = std::atoi(r);
-  }
+  msharp::Bootstrap::rank_from_env(&rank, nullptr, nullptr);
   std::unique_ptr<msharp::Bootstrap> comm;
   try {
     const msharp::Config cfg = msharp::parse_config(argc, argv);
@@ -129,6 +124,14 @@ int main(int argc, char** argv) {
     }
     if (!cfg.hub_address.empty()) {
       opt.address = cfg.hub_address;
+    }
+    if (opt.address.empty() && opt.world > 1) {
+      // Ranks started by an external process manager on several hosts: same default as the launcher.
+      const msharp::RackConfig rack = msharp::RackConfig::load(cfg.rack_config_path);
+      const msharp::RankPlan plan = msharp::build_rank_plan(rack, cfg.rank_count.value_or(opt.world), cfg.rank_selection);
+      if (plan.slot_counts_by_host().size() > 1) {
+        opt.address = plan.target(0).control_hostname + ":" + env_or("MSHARP_HUB_PORT", "29431");
+      }
     }
     comm = msharp::Bootstrap::connect(opt);
     return msharp::run_rank(cfg, *comm, chosen_driver(), std::cout);

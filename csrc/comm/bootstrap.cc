@@ -766,20 +766,59 @@ std::unique_ptr<Bootstrap> Bootstrap::connect(const BootstrapOptions& options) {
   return std::make_unique<HubBootstrap>(options);
 }
 
+namespace {
+
+const char* nonempty_env(const char* name) {
+  const char* v = std::getenv(name);
+  return v != nullptr && *v != '\0' ? v : nullptr;
+}
+
+}  // namespace
+
+bool Bootstrap::rank_from_env(int* rank, int* world, std::string* source) {
+  // What the common process managers export for each rank they start.
+  static const char* const kPairs[][3] = {
+      {"RANK", "WORLD_SIZE", "torchrun"},
+      {"OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "Open MPI mpirun"},
+      {"PMI_RANK", "PMI_SIZE", "PMI (MPICH, Intel MPI, srun --mpi=pmi2)"},
+      {"SLURM_PROCID", "SLURM_NTASKS", "Slurm srun"},
+  };
+  for (const auto& pair : kPairs) {
+    const char* r = nonempty_env(pair[0]);
+    const char* w = nonempty_env(pair[1]);
+    if (r != nullptr && w != nullptr) {
+      if (rank != nullptr) {
+        *rank = std::atoi(r);
+      }
+      if (world != nullptr) {
+        *world = std::atoi(w);
+      }
+      if (source != nullptr) {
+        *source = pair[2];
+      }
+      return true;
+    }
+  }
+  return false;
+}
+
 BootstrapOptions Bootstrap::options_from_env() {
   BootstrapOptions opt;
   auto env_int = [](const char* name, int fallback) {
     const char* v = std::getenv(name);
     return v != nullptr && *v != '\0' ? std::atoi(v) : fallback;
   };
-  opt.rank = env_int("RANK", 0);
-  opt.world = env_int("WORLD_SIZE", 1);
-  if (const char* s = std::getenv("MSHARP_SESSION"); s != nullptr && *s != '\0') {
+  rank_from_env(&opt.rank, &opt.world, nullptr);
+  if (const char* s = nonempty_env("MSHARP_SESSION"); s != nullptr) {
     opt.session = s;
-  } else if (const char* p = std::getenv("MASTER_PORT"); p != nullptr && *p != '\0') {
+  } else if (const char* p = nonempty_env("MASTER_PORT"); p != nullptr) {
     opt.session = std::string("port") + p;
+  } else if (const char* j = nonempty_env("SLURM_JOB_ID"); j != nullptr) {
+    opt.session = std::string("slurm") + j + "." + (nonempty_env("SLURM_STEP_ID") != nullptr ? nonempty_env("SLURM_STEP_ID") : "0");
+  } else if (const char* o = nonempty_env("OMPI_MCA_ess_base_jobid"); o != nullptr) {
+    opt.session = std::string("ompi") + o;
   }
-  if (const char* a = std::getenv("MSHARP_HUB_ADDR"); a != nullptr && *a != '\0') {
+  if (const char* a = nonempty_env("MSHARP_HUB_ADDR"); a != nullptr) {
     opt.address = a;
   }
   opt.timeout_ms = env_int("MSHARP_BOOTSTRAP_TIMEOUT_MS", opt.timeout_ms);

@@ -67,9 +67,14 @@ class Bootstrap {
   int broadcast_int(int value, int root);
 
   static std::unique_ptr<Bootstrap> connect(const BootstrapOptions& options);
-  // Options from RANK / WORLD_SIZE / MSHARP_SESSION (or MASTER_PORT) / MSHARP_HUB_ADDR
+  // Options from rank_from_env() / MSHARP_SESSION (or MASTER_PORT, or the Slurm / Open MPI job id) / MSHARP_HUB_ADDR
   // (host:port, selects TCP) / MSHARP_BOOTSTRAP_TIMEOUT_MS in the environment.
   static BootstrapOptions options_from_env();
+  // Rank and world size as exported by the process manager that started this process: torchrun
+  // (RANK / WORLD_SIZE), Open MPI's mpirun (OMPI_COMM_WORLD_*), PMI launchers (PMI_RANK / PMI_SIZE)
+  // or Slurm's srun (SLURM_PROCID / SLURM_NTASKS), in that order. False when none is set. No MPI
+  // library is involved: the ranks still meet through this control plane.
+  static bool rank_from_env(int* rank, int* world, std::string* source);
 };
 
 }  // namespace msharp

@@ -49,6 +49,8 @@ void* msharp_bootstrap_connect(int rank, int world, const char* session, int tim
 // address: NULL or "" for Unix-domain sockets on one host, "host:port" for TCP across hosts.
 void* msharp_bootstrap_connect_address(int rank, int world, const char* session, const char* address, int timeout_ms);
 int msharp_bootstrap_can_pass_fds(void* bootstrap);
+// JSON: rank, world, session, address, timeout_ms, launched_by, as read from the environment.
+const char* msharp_bootstrap_env_options(void);
 void msharp_bootstrap_destroy(void* bootstrap);
 int msharp_bootstrap_barrier(void* bootstrap);
 int msharp_bootstrap_allgather(void* bootstrap, const void* send, void* recv, size_t bytes_per_rank);

@@ -53,6 +53,7 @@ _SIGNATURES = {
     "msharp_bootstrap_connect": (c_void_p, [c_int, c_int, c_char_p, c_int]),
     "msharp_bootstrap_connect_address": (c_void_p, [c_int, c_int, c_char_p, c_char_p, c_int]),
     "msharp_bootstrap_can_pass_fds": (c_int, [c_void_p]),
+    "msharp_bootstrap_env_options": (c_char_p, []),
     "msharp_bootstrap_destroy": (None, [c_void_p]),
     "msharp_bootstrap_barrier": (c_int, [c_void_p]),
     "msharp_bootstrap_allgather": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),

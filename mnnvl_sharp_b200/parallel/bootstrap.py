@@ -29,13 +29,13 @@ class Bootstrap:
 
     @classmethod
     def from_env(cls, timeout_ms: int = 60000) -> "Bootstrap":
-        """RANK / WORLD_SIZE as set by torchrun or by this package's launcher; the session name
-        comes from MSHARP_SESSION, else from MASTER_PORT. MSHARP_HUB_ADDR=host:port selects TCP
-        (rank 0 listens on that port; needed only when the ranks are on more than one host)."""
-        rank = int(os.environ.get("RANK", "0"))
-        world = int(os.environ.get("WORLD_SIZE", "1"))
-        session = os.environ.get("MSHARP_SESSION") or ("port" + os.environ.get("MASTER_PORT", "0"))
-        return cls(rank, world, session, timeout_ms, os.environ.get("MSHARP_HUB_ADDR"))
+        """Rank and world size as exported by torchrun (RANK / WORLD_SIZE), mpirun, a PMI launcher or
+        srun; session from MSHARP_SESSION, else MASTER_PORT, else the Slurm / Open MPI job id.
+        MSHARP_HUB_ADDR=host:port selects TCP (rank 0 listens on that port; needed only when the
+        ranks are on more than one host). The rules live in the native library so that the
+        benchmark binary and this package agree."""
+        opt = N.as_json(N.lib.msharp_bootstrap_env_options())
+        return cls(opt["rank"], opt["world"], opt["session"], timeout_ms, opt["address"] or None)
 
     @classmethod
     def from_process_group(cls, group=None, timeout_ms: int = 60000, address: str | None = None) -> "Bootstrap":

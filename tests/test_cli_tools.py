@@ -170,6 +170,45 @@ def test_multi_host_launch_reports_a_host_that_has_no_ranks(tmp_path, monkeypatc
     assert done.returncode == 1 and "none of its ranks is on this host ('elsewhere')" in done.stderr
 
 
+def test_ranks_started_by_mpirun_or_srun_are_recognised(tmp_path):
+    """No MPI library is linked, but the rank variables that mpirun, PMI launchers and srun export are
+    read, so `mpirun -np N mnnvl_sharp_allreduce ...` works as it does for the reference binary."""
+    import subprocess
+
+    from mnnvl_sharp_b200 import _build
+
+    exe = _build.build_native()["exe"]
+    probe = [sys.executable, "-c", "from mnnvl_sharp_b200 import _native as N; import json; "
+             "print(json.dumps(N.as_json(N.lib.msharp_bootstrap_env_options())))"]
+    base = {k: v for k, v in os.environ.items()
+            if k not in ("RANK", "WORLD_SIZE", "MASTER_PORT", "MSHARP_SESSION", "MSHARP_HUB_ADDR") and not k.startswith(("OMPI_", "PMI_", "SLURM_"))}
+    base["PYTHONPATH"] = str(Path(__file__).resolve().parents[1])
+
+    def options(**env):
+        return json.loads(subprocess.run(probe, env=dict(base, **env), capture_output=True, text=True, check=True).stdout)
+
+    assert options()["world"] == 1 and options()["launched_by"].startswith("nothing")
+    o = options(PMI_RANK="2", PMI_SIZE="4")
+    assert (o["rank"], o["world"]) == (2, 4) and "PMI" in o["launched_by"]
+    o = options(SLURM_PROCID="5", SLURM_NTASKS="16", SLURM_JOB_ID="123", SLURM_STEP_ID="2")
+    assert (o["rank"], o["world"], o["session"]) == (5, 16, "slurm123.2")
+    o = options(SLURM_PROCID="5", SLURM_NTASKS="16", RANK="1", WORLD_SIZE="2", MASTER_PORT="29511", MSHARP_HUB_ADDR="10.0.0.1:4000")
+    assert (o["rank"], o["world"], o["session"], o["address"]) == (1, 2, "port29511", "10.0.0.1:4000")  # torchrun wins
+
+    rack_path = tmp_path / "rack.yaml"
+    rack_path.write_text("rack:\n  - tray:\n      - hostname: 127.0.0.1\n      - device: [0, 1]\n")
+    common = dict(base, MSHARP_DRIVER="fake", MNNVL_HOST_LABEL="tray", OMPI_COMM_WORLD_SIZE="2",
+                  OMPI_MCA_ess_base_jobid=f"{os.getpid()}", MSHARP_BOOTSTRAP_TIMEOUT_MS="20000")
+    args = [str(exe), "--rack-config", str(rack_path), "--init-only", "--json", "--no-pin", "--bytes", "2097152",
+            "--reference-check-bytes", "4096"]
+    procs = [subprocess.Popen(args, env=dict(common, OMPI_COMM_WORLD_RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=60) for p in procs]
+    assert [p.returncode for p in procs] == [0, 0], outs
+    report = json.loads(outs[0][0].strip().splitlines()[-1])
+    assert report["selected_rank_count"] == 2 and report["handle_type"] == "posix_fd" and outs[1][0].strip() == ""
+
+
 def test_preflight_helpers(tmp_path):
     text = "# comment\n10.0.0.1   # tray a\n\n  10.0.0.2\n10.0.0.1\n"
     assert preflight.normalize_nodes_config(text) == ["10.0.0.1", "10.0.0.1", "10.0.0.2"]
