@@ -475,6 +475,20 @@ int msharp_comm_set_timeout_ms(void* comm, int ms) {
   return guarded([&] { static_cast<CommHandle*>(comm)->ctx->set_timeout_ms(ms); });
 }
 
+int msharp_comm_set_trace(void* comm, int enabled) {
+  return guarded([&] { static_cast<CommHandle*>(comm)->ctx->set_trace(enabled != 0); });
+}
+
+int msharp_comm_read_trace(void* comm, double* out_us4) {
+  return guarded([&] {
+    const msharp::CommContext::PhaseTimes p = static_cast<CommHandle*>(comm)->ctx->read_trace();
+    out_us4[0] = p.entry_barrier_us;
+    out_us4[1] = p.transfer_us;
+    out_us4[2] = p.exit_barrier_us;
+    out_us4[3] = p.total_us;
+  });
+}
+
 int msharp_comm_set_multimem_barrier(void* comm, int enabled) {
   return guarded([&] { static_cast<CommHandle*>(comm)->ctx->set_multimem_barrier(enabled != 0); });
 }

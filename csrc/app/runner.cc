@@ -309,6 +309,7 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
     }
 
     canary_smoke_test(run);
+    run.ctx->set_trace(cfg.trace_phases);
 
     if (!cfg.init_only) {
       for (int i = 0; i < cfg.warmup; ++i) {
@@ -325,6 +326,12 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
       }
       if (cfg.iters == 0) {
         run_iteration(run, false, nullptr, nullptr);  // the check below needs one result
+      }
+      if (cfg.trace_phases) {
+        const CommContext::PhaseTimes p = run.ctx->read_trace();  // stamps of the last kernel; the stream is idle
+        report.phase_entry_barrier_us = comm.allgather_double(p.entry_barrier_us);
+        report.phase_transfer_us = comm.allgather_double(p.transfer_us);
+        report.phase_exit_barrier_us = comm.allgather_double(p.exit_barrier_us);
       }
 
       uint64_t* device_hash = run.ctx->scratch_u64();

@@ -175,7 +175,7 @@ std::string usage(const char* argv0) {
      << "extensions: [--sharp-backend pull|sw_f32] [--types bf16] [--pattern reference|seeded|tagged]"
      << " [--seed N] [--acc auto|f16|f32] [--handle-type auto|posix_fd|fabric] [--grid N] [--block N]"
      << " [--unroll N] [--wait-timeout-ms 2000] [--no-pin] [--session NAME] [--hub-address HOST:PORT]"
-     << " [--reference-geometry]"
+     << " [--reference-geometry] [--trace-phases]"
      << " [--cpu-only [--dump-expected FILE]]\n";
   return os.str();
 }
@@ -244,6 +244,7 @@ Config parse_config(const std::vector<std::string>& args) {
       {"--json", &Config::json},
       {"--no-pin", &Config::no_pin},
       {"--reference-geometry", &Config::reference_geometry},
+      {"--trace-phases", &Config::trace_phases},
       {"--cpu-only", &Config::cpu_only},
   };
 
@@ -361,6 +362,7 @@ std::string config_to_json(const Config& cfg) {
   w.key("session").value(cfg.session);
   w.key("hub_address").value(cfg.hub_address);
   w.key("reference_geometry").value(cfg.reference_geometry);
+  w.key("trace_phases").value(cfg.trace_phases);
   w.key("cpu_only").value(cfg.cpu_only);
   w.end_object();
   return w.str();

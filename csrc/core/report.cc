@@ -134,6 +134,20 @@ std::string json_report(const RunReport& r) {
   w.key("grid").value(r.grid);
   w.key("block").value(r.block);
   w.key("control_init_ms").value(r.control_init_ms);
+  if (!r.phase_transfer_us.empty()) {
+    auto list = [&](const char* key, const std::vector<double>& values) {
+      w.key(key).begin_array();
+      for (double v : values) {
+        w.value(v);
+      }
+      w.end_array();
+    };
+    w.key("device_phase_us_by_rank").begin_object();
+    list("entry_barrier", r.phase_entry_barrier_us);
+    list("transfer", r.phase_transfer_us);
+    list("exit_barrier", r.phase_exit_barrier_us);
+    w.end_object();
+  }
   if (r.has_results) {
     w.key("switch_model_exact_mismatches").value(static_cast<uint64_t>(r.metrics.switch_model_mismatches));
     w.key("tolerance_ulp").value(r.tolerance_ulp);

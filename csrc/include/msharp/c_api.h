@@ -74,6 +74,10 @@ int msharp_comm_clear_status(void* comm);
 int msharp_comm_reset(void* comm);  // collective
 int msharp_comm_set_timeout_ms(void* comm, int ms);
 int msharp_comm_set_multimem_barrier(void* comm, int enabled);
+// Phase stamps of collective kernels (opening barrier / data movement / closing barrier / whole
+// kernel, microseconds, as CTA 0 of this rank saw the last kernel). Read after a stream synchronise.
+int msharp_comm_set_trace(void* comm, int enabled);
+int msharp_comm_read_trace(void* comm, double* out_us4);
 
 void* msharp_symm_alloc(void* comm, size_t payload_bytes, int layout, int want_multicast);
 int msharp_symm_free(void* symm);  // collective

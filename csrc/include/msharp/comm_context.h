@@ -38,6 +38,16 @@ class CommContext {
   // Choose between multimem.red arrivals and per-peer flag stores (the latter needs no multicast).
   void set_multimem_barrier(bool enabled);
   void set_timeout_ms(int ms);
+  // Phase stamps (see kTraceStamps): switch them on, then read those of the last collective kernel
+  // after synchronising its stream. Durations in microseconds: opening barrier (waiting for the
+  // slowest peer to arrive), data movement of CTA 0, closing barrier (waiting for the slowest CTA
+  // anywhere to finish), and the whole kernel as CTA 0 saw it.
+  void set_trace(bool enabled) { device_.trace = enabled ? 1 : 0; }
+  bool trace_enabled() const { return device_.trace != 0; }
+  struct PhaseTimes {
+    double entry_barrier_us = 0, transfer_us = 0, exit_barrier_us = 0, total_us = 0;
+  };
+  PhaseTimes read_trace() const;
 
   // Blocking reads / resets of the status words (stream must be idle or synchronised by the caller).
   DeviceStatus read_status() const;

@@ -52,6 +52,7 @@ struct Config {
   bool no_pin = false;         // skip NUMA pinning
   std::string session;         // bootstrap session name (default derived from the launcher pid)
   std::string hub_address;     // host:port of rank 0's TCP control socket; needed when the plan spans hosts
+  bool trace_phases = false;   // kernels record phase stamps; the report splits the last iteration per rank
   bool reference_geometry = false;  // run the rank-0-only scalar launch shape of the reference
   bool cpu_only = false;       // oracle only: no GPU, synthetic ranks reduced on the host
   std::string dump_expected;   // with --cpu-only: file that receives the expected result bytes (cast of the float32 sum)

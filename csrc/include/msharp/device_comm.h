@@ -19,7 +19,13 @@ constexpr uint64_t kCtrlPeerTableOffset = 1536ull << 10;   // u64[kMaxWorld]: co
 constexpr uint64_t kCtrlEpochOffset = kCtrlPeerTableOffset + 4096;    // u32[kMaxBarrierSlots], local use
 constexpr uint64_t kCtrlStatusOffset = kCtrlPeerTableOffset + 32768;  // u32[16], local use
 constexpr uint64_t kCtrlScratchOffset = 1792ull << 10;     // small results (hash, canary verdict)
+constexpr uint64_t kCtrlTraceOffset = kCtrlScratchOffset + 4096;  // u64[kTraceStamps]: %globaltimer stamps of CTA 0
 constexpr uint64_t kCtrlBytes = 2ull << 20;
+
+// Phase stamps that a collective kernel leaves when DeviceComm::trace is set (CTA 0, nanoseconds of
+// %globaltimer): kernel entry, opening barrier passed, this CTA's share of the data moved, closing
+// barrier passed. The differences split a collective's time into waiting for peers and moving data.
+constexpr int kTraceStamps = 4;
 
 enum StatusBits : uint32_t {
   kStatusOk = 0,
@@ -38,6 +44,7 @@ struct DeviceComm {
   unsigned char* ctrl_mc = nullptr;     // multicast alias of all control blocks, or null
   unsigned long long timeout_ns = 2000000000ull;
   int use_multimem_barrier = 0;         // 1: multimem.red arrivals; 0: one flag store per peer
+  int trace = 0;                        // 1: CTA 0 records the phase stamps described above
 };
 
 }  // namespace msharp

@@ -45,6 +45,8 @@ struct RunReport {
   int grid = 0;
   int block = 0;
   double control_init_ms = 0.0;
+  // with --trace-phases: per rank, microseconds of the last measured iteration as CTA 0 saw them
+  std::vector<double> phase_entry_barrier_us, phase_transfer_us, phase_exit_barrier_us;
 };
 
 double algbw_gb_s(std::size_t bytes, double ms);                  // bytes / time, 1e9 bytes per GB

@@ -48,9 +48,11 @@ template <int KIND, int UNROLL>
 __global__ void __launch_bounds__(1024)
 allreduce_pull_kernel(DeviceComm comm, uint4* __restrict__ data, std::size_t vectors, std::size_t tail_words) {
   constexpr bool kLocal = KIND == dev::kReduceLocalCopy;
+  dev::trace_stamp(comm, 0);
   if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
     return;
   }
+  dev::trace_stamp(comm, 1);
   dev::fence_proxy_alias();  // inputs were written through the unicast mapping
 
   const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
@@ -81,7 +83,9 @@ allreduce_pull_kernel(DeviceComm comm, uint4* __restrict__ data, std::size_t vec
     dev::st_all_b32<kLocal>(word, dev::ld_reduce_b32<KIND>(word));
   }
   dev::fence_proxy_alias();
+  dev::trace_stamp(comm, 2);
   dev::grid_peers_barrier(comm, kStatusExitTimeout);
+  dev::trace_stamp(comm, 3);
 }
 
 template <int KIND>
@@ -129,9 +133,11 @@ allreduce_sw_f32_kernel(DeviceComm comm, PeerPointers slots, uint4* mc_data, std
   for (int r = threadIdx.x; r < comm.world; r += blockDim.x) {
     s_scale[r] = in_scales != nullptr ? in_scales[r] : 1.0f;
   }
+  dev::trace_stamp(comm, 0);
   if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
     return;
   }
+  dev::trace_stamp(comm, 1);
   const std::size_t per_rank = (vectors + comm.world - 1) / comm.world;
   const std::size_t begin = std::min(vectors, per_rank * comm.rank);
   const std::size_t end = std::min(vectors, begin + per_rank);
@@ -216,7 +222,9 @@ allreduce_sw_f32_kernel(DeviceComm comm, PeerPointers slots, uint4* mc_data, std
     }
   }
   dev::fence_proxy_alias();
+  dev::trace_stamp(comm, 2);
   dev::grid_peers_barrier(comm, kStatusExitTimeout);
+  dev::trace_stamp(comm, 3);
 }
 
 // ------------------------------------------------------------------------------------ bulk push
@@ -300,6 +308,7 @@ allreduce_bulk_push_kernel(DeviceComm comm, const unsigned char* __restrict__ in
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
 
+  dev::trace_stamp(comm, 0);  // for this kernel the first interval also holds the local copy of phase 1
   // phase 1: own replica starts as a copy of the own input (generic proxy, all threads)
   for (std::size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
     const std::size_t off = t * kBulkTileBytes;
@@ -314,6 +323,7 @@ allreduce_bulk_push_kernel(DeviceComm comm, const unsigned char* __restrict__ in
   if (!dev::grid_peers_barrier(comm, kStatusEntryTimeout)) {
     return;
   }
+  dev::trace_stamp(comm, 1);
   if (comm.world == 1) {
     return;
   }
@@ -361,7 +371,9 @@ allreduce_bulk_push_kernel(DeviceComm comm, const unsigned char* __restrict__ in
     bulk_wait_all();  // every add has been performed at its destination
   }
   __syncthreads();
+  dev::trace_stamp(comm, 2);
   dev::grid_peers_barrier(comm, kStatusExitTimeout);
+  dev::trace_stamp(comm, 3);
 }
 
 // ------------------------------------------------------------------------------------ launch helpers

@@ -112,6 +112,20 @@ __device__ __forceinline__ void st_all_b32(void* mc, uint32_t v) {
   }
 }
 
+// ---- phase trace ------------------------------------------------------------------------------
+// With tracing on, the whole CTA first meets at a CTA barrier (so that the stamp means "every
+// thread of CTA 0 got here"), then thread 0 of CTA 0 stores the time. `c.trace` is uniform over
+// the grid, so the barrier is reached by all threads or by none. Off: one predictable branch.
+__device__ __forceinline__ void trace_stamp(const DeviceComm& c, int index) {
+  if (c.trace == 0) {
+    return;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    reinterpret_cast<unsigned long long*>(c.ctrl_local + kCtrlTraceOffset)[index] = global_timer_ns();
+  }
+}
+
 // ---- status -----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t* status_words(const DeviceComm& c) {
   return reinterpret_cast<uint32_t*>(c.ctrl_local + kCtrlStatusOffset);

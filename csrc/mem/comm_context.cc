@@ -133,6 +133,20 @@ DeviceStatus CommContext::read_status() const {
   return DeviceStatus{words[0], words[1], words[2]};
 }
 
+CommContext::PhaseTimes CommContext::read_trace() const {
+  unsigned long long t[kTraceStamps] = {0, 0, 0, 0};
+  copy_out(fake_, t, device_.ctrl_local + kCtrlTraceOffset, sizeof(t));
+  PhaseTimes p;
+  if (t[0] == 0 || t[3] < t[0]) {
+    return p;  // no traced kernel has run (or it gave up before its last stamp)
+  }
+  p.entry_barrier_us = static_cast<double>(t[1] - t[0]) * 1e-3;
+  p.transfer_us = static_cast<double>(t[2] - t[1]) * 1e-3;
+  p.exit_barrier_us = static_cast<double>(t[3] - t[2]) * 1e-3;
+  p.total_us = static_cast<double>(t[3] - t[0]) * 1e-3;
+  return p;
+}
+
 void CommContext::clear_status() { fill_zero(fake_, device_.ctrl_local + kCtrlStatusOffset, 64); }
 
 void CommContext::throw_if_failed(const char* what) const {

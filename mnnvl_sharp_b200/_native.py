@@ -73,6 +73,8 @@ _SIGNATURES = {
     "msharp_comm_reset": (c_int, [c_void_p]),
     "msharp_comm_set_timeout_ms": (c_int, [c_void_p, c_int]),
     "msharp_comm_set_multimem_barrier": (c_int, [c_void_p, c_int]),
+    "msharp_comm_set_trace": (c_int, [c_void_p, c_int]),
+    "msharp_comm_read_trace": (c_int, [c_void_p, POINTER(c_double)]),
     "msharp_symm_alloc": (c_void_p, [c_void_p, c_size_t, c_int, c_int]),
     "msharp_symm_free": (c_int, [c_void_p]),
     "msharp_symm_info": (c_char_p, [c_void_p]),

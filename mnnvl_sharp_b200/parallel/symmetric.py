@@ -94,6 +94,19 @@ class Communicator:
     def set_multimem_barrier(self, enabled: bool) -> None:
         N.check(N.lib.msharp_comm_set_multimem_barrier(self._h, 1 if enabled else 0))
 
+    def set_trace(self, enabled: bool) -> None:
+        """Make the all-reduce kernels record when CTA 0 entered, passed the opening barrier, finished
+        its share of the data and passed the closing barrier (`%globaltimer`)."""
+        N.check(N.lib.msharp_comm_set_trace(self._h, 1 if enabled else 0))
+
+    def phase_times_us(self) -> dict:
+        """The stamps of the last traced kernel as durations; call after synchronising its stream.
+        entry_barrier: waiting for the last peer to arrive; transfer: moving this CTA's share;
+        exit_barrier: waiting for the slowest CTA of any rank to finish."""
+        out = (ctypes.c_double * 4)()
+        N.check(N.lib.msharp_comm_read_trace(self._h, out))
+        return {"entry_barrier_us": out[0], "transfer_us": out[1], "exit_barrier_us": out[2], "total_us": out[3]}
+
     def alloc(self, payload_bytes: int, layout: str = "single", multicast: bool = True) -> "SymmetricBuffer":
         buf = SymmetricBuffer(self, payload_bytes, layout, multicast)
         self._buffers.append(buf)

@@ -82,6 +82,24 @@ def case_allreduce_flag_barrier(comm, boot):
     return {"ok": same and same2 and m.requantized_mismatches == 0 and m2.exact_mismatches == 0}
 
 
+def case_phase_trace(comm, boot):
+    """Kernels leave their phase stamps when asked to; the parts add up and the result is unchanged."""
+    out = {}
+    ok = True
+    for backend, dtype, layout, mc in [("pull", "f16", "single", True), ("sw_f32", "e4m3", "single", True),
+                                       ("tma_async", "f16", "input_output", False)]:
+        comm.set_trace(True)
+        m, same = check_allreduce(comm, boot, backend, dtype, "tagged", 8 << 20, layout, mc)
+        p = comm.phase_times_us()
+        comm.set_trace(False)
+        parts = p["entry_barrier_us"] + p["transfer_us"] + p["exit_barrier_us"]
+        good = (same and m.exact_mismatches == 0 and p["total_us"] > 0 and min(p.values()) >= 0
+                and abs(parts - p["total_us"]) < 1e-3 and p["total_us"] < 1e6)
+        out[backend] = p
+        ok = ok and good
+    return {"ok": ok, "phases": out}
+
+
 def case_gemm_allreduce(comm, boot):
     ok = True
     detail = []

@@ -58,7 +58,7 @@ def results_of(outs):
 
 
 @needs_two
-@pytest.mark.parametrize("case", ["allreduce_exact", "allreduce_seeded", "allreduce_flag_barrier", "gemm_allreduce", "models"])
+@pytest.mark.parametrize("case", ["allreduce_exact", "allreduce_seeded", "allreduce_flag_barrier", "phase_trace", "gemm_allreduce", "models"])
 def test_multi_gpu_case(case):
     rows = results_of(run_workers(case, _world()))
     for r in rows:
