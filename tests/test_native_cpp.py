@@ -17,3 +17,30 @@ def test_native_cpp_suite_under_address_and_ub_sanitizers():
     proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert proc.returncode == 0, proc.stdout + proc.stderr
     assert "all native tests passed" in proc.stdout
+
+
+def test_cmake_build_and_ctest(tmp_path):
+    """The CMake route builds the same library, binary and tests for sm_100a and its ctest passes."""
+    import os
+    import shutil
+
+    import pytest
+
+    if shutil.which("cmake") is None:
+        pytest.skip("cmake is not installed")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    build = tmp_path / "cmake"
+    generator = ["-G", "Ninja"] if shutil.which("ninja") else []
+    configure = subprocess.run(["cmake", "-S", root, "-B", str(build), *generator], capture_output=True, text=True, timeout=300)
+    assert configure.returncode == 0, configure.stdout + configure.stderr
+    assert "multimem bulk store-reduce assembled by this nvcc" in configure.stdout
+    compile_ = subprocess.run(["cmake", "--build", str(build), "-j", str(os.cpu_count() or 4)], capture_output=True, text=True,
+                              timeout=1500)
+    assert compile_.returncode == 0, (compile_.stdout + compile_.stderr)[-4000:]
+    assert (build / "libmsharp.so").exists() and (build / "mnnvl_sharp_allreduce").exists()
+    ninja = build / "build.ninja"
+    if ninja.exists():
+        text = ninja.read_text()
+        assert "arch=compute_100a,code=sm_100a" in text and "compute_52" not in text and "sm_90" not in text
+    tests = subprocess.run(["ctest", "--test-dir", str(build), "--output-on-failure"], capture_output=True, text=True, timeout=600)
+    assert tests.returncode == 0 and "100% tests passed" in tests.stdout, tests.stdout + tests.stderr
