@@ -81,6 +81,19 @@ def test_missing_rack_config_and_help_print_usage():
     assert "[--rank-selection balanced|prefix] [--sharp-backend legacy|tma_async]" in rack.usage()
 
 
+def test_extension_flags_are_parsed_and_listed_in_usage():
+    cfg = rack.parse_cli(["--rack-config", "r.yaml", "--trace-phases", "--hub-address", "10.0.0.1:4000", "--session", "job7",
+                          "--handle-type", "fabric", "--wait-timeout-ms", "500", "--no-pin"])
+    assert cfg["trace_phases"] is True and cfg["hub_address"] == "10.0.0.1:4000" and cfg["session"] == "job7"
+    assert cfg["handle_type"] == "fabric" and cfg["wait_timeout_ms"] == 500 and cfg["no_pin"] is True
+    defaults = rack.parse_cli(["--rack-config", "r.yaml"])
+    assert defaults["trace_phases"] is False and defaults["hub_address"] == "" and defaults["handle_type"] == "auto"
+    for flag in ("--trace-phases", "--hub-address HOST:PORT", "--handle-type auto|posix_fd|fabric", "--cpu-only"):
+        assert flag in rack.usage(), flag
+    with pytest.raises(NativeError, match="--hub-address"):
+        rack.parse_cli(["--rack-config", "r.yaml", "--hub-address"])
+
+
 RACK_2X4 = """
 # two trays
 rack:
