@@ -76,3 +76,43 @@ class TensorParallelFFNDown(torch.nn.Module):
 
     def forward(self, gate_local: torch.Tensor, up_local: torch.Tensor) -> torch.Tensor:
         return self.down(torch.nn.functional.silu(gate_local.float()) * up_local.float())
+
+
+class TensorParallelFFN(torch.nn.Module):
+    """A whole gated FFN block (Llama style) under tensor parallelism.
+
+    The gate and up projections are column-parallel: every rank holds `intermediate / world`
+    output columns of each and multiplies the full input by them (BF16 library GEMM: no
+    communication is needed there). SiLU(gate) * up stays local, is quantised to FP8 with
+    1 x 128 block scales, and goes through the row-parallel down-projection whose all-reduce is
+    fused into the GEMM kernel. One in-switch reduction per block, no other traffic."""
+
+    def __init__(self, comm: Communicator, hidden: int, intermediate: int, max_tokens: int, seed: int = 0):
+        super().__init__()
+        if intermediate % (comm.world * BLOCK):
+            raise ValueError("intermediate / world must be a multiple of 128")
+        self.comm = comm
+        self.hidden = hidden
+        self.local_cols = intermediate // comm.world
+        g = torch.Generator(device="cuda").manual_seed(seed + 1)  # full weights on every rank, then sliced
+        gate = torch.randn(intermediate, hidden, device="cuda", generator=g) / hidden ** 0.5
+        up = torch.randn(intermediate, hidden, device="cuda", generator=g) / hidden ** 0.5
+        rows = slice(comm.rank * self.local_cols, (comm.rank + 1) * self.local_cols)
+        self.register_buffer("gate_weight", gate[rows].to(torch.bfloat16).contiguous())
+        self.register_buffer("up_weight", up[rows].to(torch.bfloat16).contiguous())
+        self.down = RowParallelLinearFP8(comm, intermediate, hidden, max_tokens, seed=seed)
+
+    def local_activation(self, x: torch.Tensor) -> torch.Tensor:
+        xb = x.to(torch.bfloat16)
+        return torch.nn.functional.silu((xb @ self.gate_weight.t()).float()) * (xb @ self.up_weight.t()).float()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: [tokens, hidden], the same on every rank. Returns BF16 [tokens, hidden], the same on every rank."""
+        return self.down(self.local_activation(x))
+
+    def reference(self, x: torch.Tensor) -> torch.Tensor:
+        """This rank's partial result in float32 (sum over ranks = the block's output)."""
+        return self.down.reference(self.local_activation(x))
+
+    def free(self) -> None:
+        self.down.free()

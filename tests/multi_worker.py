@@ -132,7 +132,7 @@ def case_gemm_allreduce(comm, boot):
 
 
 def case_models(comm, boot):
-    from mnnvl_sharp_b200.models import GradientAllReducer, RowParallelLinearFP8
+    from mnnvl_sharp_b200.models import GradientAllReducer, RowParallelLinearFP8, TensorParallelFFN
 
     world = comm.world
     layer = RowParallelLinearFP8(comm, in_features=128 * 4 * world, out_features=384, max_tokens=256, seed=5)
@@ -149,6 +149,22 @@ def case_models(comm, boot):
     ok = err <= float(np.abs(total).max()) * 2 ** -6 + 1e-3
     layer.free()
 
+    # a whole gated FFN block: column-parallel gate / up, local SiLU * up, fused row-parallel down-projection
+    ffn = TensorParallelFFN(comm, hidden=256, intermediate=128 * 2 * world, max_tokens=128, seed=9)
+    torch.manual_seed(33)
+    tokens = torch.randn(128, 256, device="cuda")
+    boot.barrier()
+    z = ffn(tokens).float()
+    torch.cuda.synchronize()
+    boot.barrier()
+    comm.raise_if_failed("tensor-parallel FFN")
+    want = boot.allgather_array(ffn.reference(tokens).cpu().numpy()).sum(axis=0)
+    ffn_err = float(np.abs(z.cpu().numpy() - want).max())
+    z16 = z.to(torch.bfloat16).contiguous()  # named: the hash kernel reads it after this statement
+    hashes = boot.allgather_array(np.array([ops.device_hash(z16.data_ptr(), z16.numel() * 2)], dtype=np.uint64))[:, 0]
+    ok = ok and ffn_err <= float(np.abs(want).max()) * 2 ** -6 + 1e-3 and len(set(int(h) for h in hashes)) == 1
+    ffn.free()
+
     model = torch.nn.Linear(48, 16).cuda()
     for p in model.parameters():
         p.grad = torch.full_like(p, float(comm.rank + 1))
@@ -161,7 +177,7 @@ def case_models(comm, boot):
     want = (world + 1) / 2.0
     ok = ok and all(torch.allclose(p.grad, torch.full_like(p, want)) for p in model.parameters())
     reducer.free()
-    return {"ok": ok, "linear_err": err}
+    return {"ok": ok, "linear_err": err, "ffn_err": ffn_err}
 
 
 def case_absent_peer(comm, boot):
