@@ -25,7 +25,17 @@ OBJ = ROOT / "build" / "obj"
 
 NVCC = os.environ.get("MNNVL_CUDA_COMPILER", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
 CUDA_HOME = Path(NVCC).resolve().parent.parent
-GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
+def _gencode() -> list[str]:
+    """MNNVL_CUDA_ARCHITECTURES is the reference launcher's knob (scripts/run_mnnvl_sharp.sh:66, default
+    100a). The kernels here are written for sm_100a alone (tcgen05, FP8 multimem forms), so any other
+    value is refused with the reason instead of producing a build that cannot run."""
+    arch = os.environ.get("MNNVL_CUDA_ARCHITECTURES", "100a").strip()
+    if arch not in ("100a", "sm_100a"):
+        raise RuntimeError(f"MNNVL_CUDA_ARCHITECTURES={arch!r}: this package builds for 100a (B200, sm_100a) only")
+    return ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+GENCODE = _gencode()
 CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra", "-g1"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"] + GENCODE
 INCLUDES = ["-I", str(CSRC / "include"), "-I", str(CSRC / "kernels"), "-I", str(CUDA_HOME / "include")]
