@@ -125,7 +125,7 @@ msharp::PeerPointers outputs_of(const msharp::SymmetricMemory& m, std::size_t of
 }
 
 void check_range(const msharp::SymmetricMemory& m, std::size_t offset, std::size_t bytes) {
-  if (offset % 16 != 0 || bytes == 0 || offset + bytes > m.payload_bytes) {
+  if (offset % 16 != 0 || bytes == 0 || offset > m.payload_bytes || bytes > m.payload_bytes - offset) {
     throw std::invalid_argument("range must start on a 16-byte boundary and lie inside the payload");
   }
 }

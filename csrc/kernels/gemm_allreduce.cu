@@ -581,14 +581,6 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
       throw std::runtime_error("gemm_allreduce: workspace address of rank " + std::to_string(r) + " is missing");
     }
   }
-  const int sms = device_sm_count();
-  // The grid is always one CTA per SM so that the reducer CTAs (which wait for their peers) are
-  // resident and so that the same barrier slots are used by every launch.
-  const int grid = sms;
-  // 32 reducer CTAs keep up with the tile rate at any world size (one tile per switch round trip
-  // each); more only add queued requests, and every CTA reducing was measured to stall at 2 ranks.
-  p.reducer_ctas = std::min(std::min(grid, 64), a.reducer_ctas > 0 ? a.reducer_ctas : 32);
-
   // 128-wide tiles are the default: measured on B200 at 8192 x 8192 x 3584 they take 0.42 ms against
   // 0.78 ms for 256-wide tiles (two accumulators instead of four, twice the promotion work per
   // thread); the wide tile stays selectable for shapes where it may pay.
@@ -599,6 +591,14 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
   if (a.n % tile_n != 0) {
     throw std::runtime_error("gemm_allreduce: N is not a multiple of the requested tile width");
   }
+  const int sms = device_sm_count();
+  // The grid is always one CTA per SM so that the reducer CTAs (which wait for their peers) are
+  // resident and so that the same barrier slots are used by every launch.
+  const int grid = sms;
+  // 32 reducer CTAs keep up with the tile rate at any world size (one tile per switch round trip
+  // each); more only add queued requests, and every CTA reducing was measured to stall at 2 ranks.
+  p.reducer_ctas = std::min(std::min(grid, 64), a.reducer_ctas > 0 ? a.reducer_ctas : 32);
+
   const CUtensorMap map_a = make_tile_map(api, a.a, a.m, a.k, BM);
   const CUtensorMap map_w = make_tile_map(api, a.w, a.n, a.k, tile_n);
   auto launch = [&](auto kernel) {

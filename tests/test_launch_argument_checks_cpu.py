@@ -1,0 +1,83 @@
+"""Argument checks of the collective launchers, reached without a GPU.
+
+Every launcher validates its arguments on the host before it touches the CUDA runtime
+(alignment, size multiples, ranges inside the payload, layout and shape rules). With the
+host-memory driver stand-in a communicator and buffers exist on a machine without GPUs, so the
+refusals can be checked here; the accepted cases run in the GPU suites.
+"""
+import ctypes
+
+import pytest
+
+from mnnvl_sharp_b200 import _native as N
+from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+
+
+@pytest.fixture()
+def solo():
+    N.lib.msharp_fake_driver_reset(8)
+    boot = Bootstrap(0, 1, "argcheck")
+    comm = Communicator(boot, 0, fake_driver=True)
+    yield comm
+    comm.close()
+    boot.close()
+
+
+def refused(rc: int) -> str:
+    assert rc != 0, "the call was accepted"
+    return N.last_error()
+
+
+def test_all_reduce_ranges_must_be_aligned_and_inside_the_payload(solo):
+    buf = solo.alloc(1 << 20)
+    lib = N.lib
+    assert "16-byte boundary" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, 8, 1024, 0, 0, 0, 0))
+    assert "inside the payload" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, 0, (1 << 20) + 16, 0, 0, 0, 0))
+    assert "inside the payload" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, 0, 0, 0, 0, 0, 0))
+    # an offset near the top of the address space must not wrap around the bound check
+    huge = (1 << 64) - 16
+    assert "inside the payload" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, huge, 32, 0, 0, 0, 0))
+    assert "inside the payload" in refused(lib.msharp_allreduce_sw_f32(solo.handle, buf.handle, huge, 32, 0, 1.0, 0, 0, 0))
+    assert "multiple of 4" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, 0, 1022, 0, 0, 0, 0))
+    assert "unroll must be" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 0, 0, 0, 1024, 0, 0, 3, 0))
+    assert "dtype must be" in refused(lib.msharp_allreduce_pull(solo.handle, buf.handle, 7, 0, 0, 1024, 0, 0, 0, 0))
+
+
+def test_bulk_push_needs_the_two_region_layout_a_16_byte_size_and_a_16_bit_type(solo):
+    single = solo.alloc(1 << 20)
+    assert "out of place" in refused(N.lib.msharp_allreduce_bulk_push(solo.handle, single.handle, 1, 0, 4096, 0, 0))
+    both = solo.alloc(1 << 20, layout="input_output")
+    assert "multiple of 16" in refused(N.lib.msharp_allreduce_bulk_push(solo.handle, both.handle, 1, 0, 4100, 0, 0))
+    assert "no FP8 form" in refused(N.lib.msharp_allreduce_bulk_push(solo.handle, both.handle, 0, 0, 4096, 0, 0))
+
+
+def test_reference_geometry_needs_a_multicast_alias(solo):
+    buf = solo.alloc(1 << 20)  # one rank: no alias
+    assert "multicast alias" in refused(N.lib.msharp_allreduce_reference_geometry(buf.handle, 0, 4096, 0))
+
+
+def test_fused_gemm_shape_alignment_and_buffer_rules(solo):
+    out = solo.alloc(256 * 256 * 2)
+    host = (ctypes.c_uint8 * 4096)()
+    ptr = (ctypes.addressof(host) + 15) & ~15  # any aligned, non-null address: the checks come before any access
+    lib = N.lib
+
+    def gemm(m, n, k, a=ptr, w=ptr, sa=ptr, sw=ptr, reducers=0):
+        return lib.msharp_gemm_allreduce(solo.handle, out.handle, a, sa, w, sw, m, n, k, reducers, 0)
+
+    assert "smaller than m * n" in refused(gemm(512, 256, 128))
+    assert "multiples of 128" in refused(gemm(256, 256, 100))
+    assert "multiples of 128" in refused(gemm(200, 256, 128))
+    assert "multiples of 128" in refused(gemm(0, 256, 128))
+    assert "16-byte aligned" in refused(gemm(256, 256, 128, a=ptr + 4))
+    assert "non-null" in refused(gemm(256, 256, 128, sa=0))
+    assert "tile width" in refused(gemm(128, 128, 128, reducers=(256 << 16)))  # N = 128 cannot hold a 256-wide tile
+
+
+def test_status_words_and_trace_read_back_as_idle_before_any_kernel(solo):
+    assert solo.status().ok
+    assert solo.phase_times_us() == {"entry_barrier_us": 0.0, "transfer_us": 0.0, "exit_barrier_us": 0.0, "total_us": 0.0}
+    solo.set_trace(True)
+    solo.set_trace(False)
+    with pytest.raises(N.NativeError, match="multicast alias"):
+        solo.set_multimem_barrier(True)  # a world of one rank has no alias to signal through
