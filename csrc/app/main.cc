@@ -56,9 +56,11 @@ std::string short_host_name() {
   return msharp::normalize_host_label(buf);
 }
 
-// MSHARP_DRIVER=fake runs the host side of a rank (plan, topology checks, control plane, memory
-// set-up, canary, report) against the host-memory stand-in for the driver; only --init-only runs
-// that way. It exists so that launch and multi-host logic can be exercised on machines without GPUs.
+// MSHARP_DRIVER=fake runs a rank against the host-memory stand-in for the driver: plan, topology
+// checks, control plane, memory set-up and canary as on a GPU, and the collective itself played
+// through on the CPU over the shared mappings (float32 sum, one cast; see runner.cc). It exists so
+// that launch, multi-host and reporting logic can be exercised on machines without GPUs; its
+// timings mean nothing and the report says "host_emulation_f32_sum".
 const msharp::DriverApi& chosen_driver() {
   if (env_or("MSHARP_DRIVER", "real") != "fake") {
     return msharp::real_driver();
@@ -136,7 +138,11 @@ int main(int argc, char** argv) {
     comm = msharp::Bootstrap::connect(opt);
     return msharp::run_rank(cfg, *comm, chosen_driver(), std::cout);
   } catch (const std::exception& ex) {
-    std::cerr << "rank " << rank << " error: " << ex.what() << "\n";
+    // one write, so that the lines of ranks that fail together do not interleave
+    const std::string line = "rank " + std::to_string(rank) + " error: " + ex.what() + "\n";
+    if (::write(STDERR_FILENO, line.data(), line.size()) < 0) {
+      std::cerr << line;
+    }
     if (comm) {
       comm->abort(ex.what());
     }

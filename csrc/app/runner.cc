@@ -16,13 +16,16 @@
 #include <cuda_runtime_api.h>
 #include <nvtx3/nvToolsExt.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
+#include <cstring>
 #include <fstream>
 #include <iostream>
 #include <memory>
 #include <sstream>
 #include <stdexcept>
+#include <vector>
 
 #include "msharp/comm_context.h"
 #include "msharp/json.h"
@@ -131,8 +134,70 @@ void canary_smoke_test(RankRun& run) {
   run.comm.barrier();
 }
 
+// ---- host emulation (driver stand-in only) ---------------------------------------------------
+// With the host-memory stand-in the "device" pointers are ordinary host pointers into memory that
+// all rank processes share, so the collective can be played through on the CPU: same slicing as
+// the kernels (rank r reduces the r-th part and writes it into every replica), float32 sum in rank
+// order and one final cast (what the sw_f32 kernel computes and what the oracle calls the float32
+// model). It exists to run the whole benchmark flow (iterations, hashes, check, report, exit code)
+// among CPU processes, on one machine or through the multi-host launch path; it measures nothing.
+void emulate_initialize(RankRun& run) {
+  const Config& cfg = run.cfg;
+  InputSpec spec;
+  spec.pattern = run.pattern;
+  spec.seed = cfg.seed;
+  spec.ranks = run.rank.world_size;
+  const std::size_t elements = cfg.bytes / dtype_size(run.dtype);
+  generate_input(run.dtype, spec, run.rank.world_rank, 0, elements, run.input_ptr());
+  if (cfg.sharp_backend == Backend::kTmaAsync) {
+    std::memset(run.output_ptr(), 0xff, cfg.bytes);  // poison, as on the device
+  }
+}
+
+void emulate_collective(RankRun& run) {
+  const Config& cfg = run.cfg;
+  const int world = run.rank.world_size;
+  const std::size_t size = dtype_size(run.dtype);
+  const std::size_t elements = cfg.bytes / size;
+  const std::size_t per_rank = (elements + static_cast<std::size_t>(world) - 1) / static_cast<std::size_t>(world);
+  const std::size_t begin = std::min(elements, per_rank * static_cast<std::size_t>(run.rank.world_rank));
+  const std::size_t end = std::min(elements, begin + per_rank);
+  run.comm.barrier();  // the opening barrier of the kernels: every rank's input is in place
+  if (end > begin) {
+    std::vector<const void*> inputs(static_cast<std::size_t>(world));
+    for (int r = 0; r < world; ++r) {
+      inputs[static_cast<std::size_t>(r)] = reinterpret_cast<const unsigned char*>(run.mem->input_ptr(r)) + begin * size;
+    }
+    std::vector<float> sums(end - begin);
+    reduce_arrays_f32(run.dtype, inputs.data(), world, end - begin, sums.data());
+    std::vector<unsigned char> slice((end - begin) * size);
+    cast_from_f32(run.dtype, sums.data(), end - begin, slice.data());
+    run.comm.barrier();  // in place: nobody overwrites a slice that a peer still reads
+    for (int r = 0; r < world; ++r) {
+      std::memcpy(reinterpret_cast<unsigned char*>(run.mem->output_ptr(r)) + begin * size, slice.data(), slice.size());
+    }
+  } else {
+    run.comm.barrier();
+  }
+  run.comm.barrier();  // the closing barrier: every slice has landed in every replica
+  // Host-side fault injection for tests of the failure path: MSHARP_FAKE_CORRUPT="rank:byte" makes
+  // that rank flip one bit of its own replica, as a lost or torn store would.
+  if (const char* spec = std::getenv("MSHARP_FAKE_CORRUPT"); spec != nullptr && *spec != '\0') {
+    char* rest = nullptr;
+    const long rank = std::strtol(spec, &rest, 10);
+    const unsigned long long byte = rest != nullptr && *rest == ':' ? std::strtoull(rest + 1, nullptr, 10) : 0ull;
+    if (rank == run.rank.world_rank && byte < cfg.bytes) {
+      static_cast<unsigned char*>(run.output_ptr())[byte] ^= 0x01u;
+    }
+  }
+}
+
 void initialize_buffers(RankRun& run) {
   const Config& cfg = run.cfg;
+  if (run.api.is_fake) {
+    emulate_initialize(run);
+    return;
+  }
   launch_init_pattern(run.dtype, run.pattern, cfg.seed, run.rank.world_rank, run.input_ptr(), cfg.bytes, run.stream);
   if (cfg.sharp_backend == Backend::kTmaAsync) {
     launch_poison_fill(run.output_ptr(), cfg.bytes, run.stream);
@@ -176,6 +241,15 @@ void run_iteration(RankRun& run, bool measure, double* device_ms, double* wall_m
   initialize_buffers(run);
   run.comm.barrier();  // every rank's input is in place
   const auto t0 = Clock::now();
+  if (run.api.is_fake) {
+    emulate_collective(run);
+    const double local = ms_since(t0);
+    if (measure) {
+      *device_ms = run.comm.reduce_max(local);
+      *wall_ms = *device_ms;
+    }
+    return;
+  }
   if (measure) {
     MSHARP_CUDA(cudaEventRecord(run.start, run.stream));
   }
@@ -220,9 +294,6 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   RankRun run{cfg, comm, api, {}, {}, nullptr, nullptr, nullptr, nullptr, nullptr, Dtype::kE4M3, 0, {}, {}, {}};
   run.rank = discover_rank_info(comm.rank(), world, rack, plan, label_env != nullptr ? label_env : "");
   const bool fake = api.is_fake;
-  if (fake && !cfg.init_only) {
-    throw std::runtime_error("the host-memory driver stand-in runs --init-only only (there is no device to reduce on)");
-  }
   if (!fake) {
     MSHARP_CUDA(cudaSetDevice(run.rank.gpu_ordinal));
     MSHARP_CUDA(cudaFree(nullptr));  // creates the primary context that the driver calls below use
@@ -308,8 +379,12 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
         break;
     }
 
+    if (fake) {
+      report.kernel_variant = "host_emulation_f32_sum";
+    }
+
     canary_smoke_test(run);
-    run.ctx->set_trace(cfg.trace_phases);
+    run.ctx->set_trace(cfg.trace_phases && !fake);
 
     if (!cfg.init_only) {
       for (int i = 0; i < cfg.warmup; ++i) {
@@ -327,18 +402,22 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
       if (cfg.iters == 0) {
         run_iteration(run, false, nullptr, nullptr);  // the check below needs one result
       }
-      if (cfg.trace_phases) {
+      if (cfg.trace_phases && !fake) {
         const CommContext::PhaseTimes p = run.ctx->read_trace();  // stamps of the last kernel; the stream is idle
         report.phase_entry_barrier_us = comm.allgather_double(p.entry_barrier_us);
         report.phase_transfer_us = comm.allgather_double(p.transfer_us);
         report.phase_exit_barrier_us = comm.allgather_double(p.exit_barrier_us);
       }
 
-      uint64_t* device_hash = run.ctx->scratch_u64();
-      launch_hash(run.output_ptr(), cfg.bytes, device_hash, run.stream);
       uint64_t local_hash = 0;
-      MSHARP_CUDA(cudaMemcpyAsync(&local_hash, device_hash, sizeof(local_hash), cudaMemcpyDeviceToHost, run.stream));
-      MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+      if (fake) {
+        local_hash = hash_words(static_cast<const uint32_t*>(run.output_ptr()), cfg.bytes / 4);
+      } else {
+        uint64_t* device_hash = run.ctx->scratch_u64();
+        launch_hash(run.output_ptr(), cfg.bytes, device_hash, run.stream);
+        MSHARP_CUDA(cudaMemcpyAsync(&local_hash, device_hash, sizeof(local_hash), cudaMemcpyDeviceToHost, run.stream));
+        MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+      }
       report.hashes = comm.allgather_u64(local_hash);
       report.has_results = true;
       report.device_ms = summarize(device_times);

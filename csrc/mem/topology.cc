@@ -45,6 +45,10 @@ RankInfo discover_rank_info(int world_rank, int world_size, const RackConfig& ra
     tray = target.rack_index;  // "localhost" stands for whatever machine this is
   }
   if (tray < 0) {
+    if (!host_label_override.empty()) {
+      throw std::runtime_error("MNNVL_HOST_LABEL '" + host_label_override + "' did not match rack.yaml (hostname '" +
+                               info.os_hostname + "')");
+    }
     throw std::runtime_error("hostname '" + info.os_hostname +
                              "' did not match rack.yaml; set MNNVL_HOST_LABEL to the rack key if the container hostname differs");
   }

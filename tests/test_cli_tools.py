@@ -112,7 +112,8 @@ def test_multi_host_launch_end_to_end_without_gpus(tmp_path, monkeypatch, capfd)
     """Two trays on "different hosts": the launcher prepares and starts each host through its ssh
     command (here a script that runs the command on this machine), every host's copy of the binary
     starts its own ranks, they meet over TCP, share memory through fabric handles (the driver
-    stand-in), pass the canary test of every slot, and rank 0 prints the report."""
+    stand-in), pass the canary test of every slot, run the iterations (the collective is played
+    through on the CPU), agree on the replica hashes, and rank 0 prints the report."""
     import json
     import socket
     import stat
@@ -143,13 +144,14 @@ def test_multi_host_launch_end_to_end_without_gpus(tmp_path, monkeypatch, capfd)
     monkeypatch.setenv("MSHARP_DRIVER", "fake")
     monkeypatch.setenv("MSHARP_FAKE_FABRIC", "1")
     monkeypatch.setenv("MSHARP_BOOTSTRAP_TIMEOUT_MS", "20000")
-    rc = run.main([str(rack_path), "--rank-count", "4", "--init-only", "--json", "--no-pin", "--bytes", "4194304",
-                   "--reference-check-bytes", "4096"])
+    rc = run.main([str(rack_path), "--rank-count", "4", "--json", "--no-pin", "--bytes", "4194304",
+                   "--reference-check-bytes", "4096", "--warmup", "1", "--iters", "2", "--pattern", "seeded"])
     out = capfd.readouterr().out
     assert rc == 0, out
     assert (app_dir / "mnnvl_sharp_b200" / "_C" / "mnnvl_sharp_allreduce").exists() and (app_dir / ".launch_rack.yaml").exists()
     report = json.loads([line for line in out.splitlines() if line.startswith("{")][-1])
-    assert report["selected_rank_count"] == 4 and report["handle_type"] == "fabric" and report["init_only"] is True
+    assert report["selected_rank_count"] == 4 and report["handle_type"] == "fabric" and report["init_only"] is False
+    assert report["hashes_match"] is True and len(report["hashes"]) == 4 and report["status"] == 0
     assert [(m["rank"], m["host_label"], m["local_rank"], m["gpu"]) for m in report["host_mapping"]] == [
         (0, "hostA", 0, 0), (1, "hostB", 0, 2), (2, "hostA", 1, 1), (3, "hostB", 1, 3)]
     assert len(report["peer_init_local_ms_by_rank"]) == 4
