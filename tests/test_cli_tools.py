@@ -72,6 +72,22 @@ def test_sweep_writes_reference_schema_resumes_and_plots(tmp_path):
     assert (out_dir / "init_latency.png").exists() or (out_dir / "init_latency.svg").exists()
 
 
+def test_sweep_through_the_real_launcher_and_binary_without_gpus(tmp_path, monkeypatch):
+    """The same sweep with nothing stubbed: launcher -> binary -> rank processes -> symmetric-memory
+    set-up (driver stand-in) -> JSON line -> CSV row and chart."""
+    monkeypatch.setenv("MSHARP_DRIVER", "fake")
+    rack_path = Path(__file__).resolve().parents[1] / "examples" / "rack_hgx8.yaml"
+    out_dir = tmp_path / "sweep"
+    assert init_sweep.main([str(rack_path), "--rank-counts", "2,4", "--repeats", "1", "--out-dir", str(out_dir)]) == 0
+    rows = list(csv.DictReader((out_dir / "init_latency.csv").open()))
+    assert [r["rank_count"] for r in rows] == ["2", "4", "8"]  # the inventory total joins the list
+    for r in rows:
+        assert float(r["peer_init_min_ms"]) <= float(r["peer_init_median_ms"]) <= float(r["peer_init_max_ms"]) == float(r["peer_init_ms"])
+    log = (out_dir / "rank_4_repeat_0.log").read_text()
+    assert "--init-only --json" in log and '"init_only":true' in log and '"selected_rank_count":4' in log
+    assert (out_dir / "init_latency.png").exists() or (out_dir / "init_latency.svg").exists()
+
+
 def test_svg_fallback_chart(tmp_path):
     svg = plot_init_latency.svg_chart({2: [1.0, 2.0, 3.0], 8: [4.0, 5.0, 9.0]})
     assert svg.startswith("<svg") and "rank count" in svg and "peer access initialization latency (ms)" in svg
