@@ -9,6 +9,7 @@
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -239,6 +240,66 @@ void test_codec_spot_checks() {
   EXPECT(reference_f16_bits(0, 0) == 0x0000);  // mix = 7 -> table entry 7
 }
 
+// Mutated inventories and CLI words through the parsers: every input must end in a value or an
+// exception, never in a crash, a hang or a sanitizer report.
+void test_parsers_survive_mutated_input() {
+  using namespace msharp;
+  const std::string base =
+      "# two trays\nrack:\n  - tray-a.example.com:\n      - hostname: 10.0.0.11\n      - port: 4399\n"
+      "      - device: [0, 1, 2, 3]\n  - tray-b:\n      hostname: \"10.0.0.12\"\n      device:\n        - 3\n        - 2\n";
+  const std::string pieces[] = {"\n", "\t", " ", "-", ":", "[", "]", "{", "}", ",", "#", "\"", "'", "|", ">", "&", "*", "!",
+                                "%", "0", "9", "a", ".", "\\", "\r", "  - ", "hostname: ", "device: ", "port: ", "rack:\n",
+                                "[0, 1]", "\n      ", "99999999999999999999", "-1", "0x10"};
+  const std::size_t piece_count = sizeof(pieces) / sizeof(pieces[0]);
+  uint64_t state = 0x9e3779b97f4a7c15ull;
+  auto next = [&](uint64_t bound) {
+    state = state * 6364136223846793005ull + 1442695040888963407ull;
+    return bound == 0 ? 0 : (state >> 33) % bound;
+  };
+  int accepted = 0;
+  int refused = 0;
+  for (int round = 0; round < 20000; ++round) {
+    std::string text = base;
+    const int edits = 1 + static_cast<int>(next(6));
+    for (int e = 0; e < edits; ++e) {
+      const uint64_t op = next(10);
+      const std::size_t pos = static_cast<std::size_t>(next(text.size() + 1));
+      if (op < 4 && !text.empty()) {
+        text.erase(std::min(pos, text.size() - 1), 1 + static_cast<std::size_t>(next(20)));
+      } else {
+        text.insert(pos, pieces[next(piece_count)]);
+      }
+    }
+    try {
+      const RackConfig rack = RackConfig::parse(text);
+      ++accepted;
+      const int total = static_cast<int>(rack.available_rank_count());
+      build_rank_plan(rack, 1 + static_cast<int>(next(static_cast<uint64_t>(total))), next(2) ? "balanced" : "prefix");
+    } catch (const std::exception&) {
+      ++refused;
+    }
+  }
+  EXPECT(accepted > 100 && refused > 100);
+  const char* words[] = {"--rack-config", "r.yaml", "--bytes", "--iters", "--types", "f16", "e4m3", "--sharp-backend", "legacy",
+                         "tma_async", "0x1000", "-5", "99999999999999999999999", "", "--json", "--init-only", "--rank-count",
+                         "--reference-check-bytes", "16", "--warmup", "3", "--help", "--pattern", "seeded", "--seed", "abc"};
+  const std::size_t word_count = sizeof(words) / sizeof(words[0]);
+  int parsed = 0;
+  for (int round = 0; round < 20000; ++round) {
+    std::vector<std::string> args = {"prog"};
+    const int n = static_cast<int>(next(9));
+    for (int i = 0; i < n; ++i) {
+      args.emplace_back(words[next(word_count)]);
+    }
+    try {
+      parse_config(args);
+      ++parsed;
+    } catch (const std::exception&) {
+    }
+  }
+  EXPECT(parsed > 0);
+}
+
 int free_tcp_port() {
   const int fd = ::socket(AF_INET, SOCK_STREAM, 0);
   sockaddr_in addr;
@@ -358,6 +419,7 @@ int main() {
   test_status_text();
   test_codec_spot_checks();
   test_tcp_control_plane_and_fabric_handles();
+  test_parsers_survive_mutated_input();
   if (g_failures == 0) {
     std::printf("all native tests passed\n");
     return 0;
