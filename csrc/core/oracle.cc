@@ -50,6 +50,110 @@ inline float load_input(Dtype dtype, const InputSpec& spec, int rank, std::size_
   return 0.0f;
 }
 
+// ---- block-wise input generation ----------------------------------------------------------------
+// The reductions walk the elements in blocks and the ranks inside a block, so that what depends on
+// the rank alone (the key of the counter-based generator) is computed once per block instead of once
+// per element, and the inner loops run over contiguous arrays. Values are bit-identical to
+// load_input(): same formulas (numerics.h counter_rng / seeded_uniform_pm2 / seeded_normal), same
+// float32 additions in rank order.
+constexpr std::size_t kBlock = 256;
+
+inline uint64_t rng_key(uint64_t seed, int rank) {
+  return mix64(seed ^ (0x9e3779b97f4a7c15ull * static_cast<uint64_t>(rank + 1)));
+}
+
+inline uint64_t rng_keyed(uint64_t key, uint64_t element, uint32_t stream) {
+  return mix64(key + element * 0xd1342543de82ef95ull + static_cast<uint64_t>(stream) * 0x2545f4914f6cdd1dull);
+}
+
+inline float uniform_pm2_keyed(uint64_t key, uint64_t element) {
+  const uint32_t u24 = static_cast<uint32_t>(rng_keyed(key, element, 0) >> 40);
+  return static_cast<float>(static_cast<int32_t>(u24) - (1 << 23)) * 2.3841857910156250e-07f;
+}
+
+inline float normal_keyed(uint64_t key, uint64_t element) {
+  int32_t sum = 0;
+  for (uint32_t s = 0; s < 3; ++s) {
+    const uint64_t r = rng_keyed(key, element, 1 + s);
+    sum += static_cast<int32_t>(r & 0xffffu) + static_cast<int32_t>((r >> 16) & 0xffffu) +
+           static_cast<int32_t>((r >> 32) & 0xffffu) + static_cast<int32_t>((r >> 48) & 0xffffu);
+  }
+  sum -= 6 * 65535;
+  return static_cast<float>(sum) * 1.52587890625e-05f;
+}
+
+// Decoded inputs of `rank` for elements [first, first + count), count <= kBlock.
+inline void load_block(Dtype dtype, const InputSpec& spec, int rank, std::size_t first, std::size_t count, float* out) {
+  if (spec.pattern == kPatternSeeded) {
+    const uint64_t key = rng_key(spec.seed, rank);
+    switch (dtype) {
+      case Dtype::kE4M3:
+        for (std::size_t i = 0; i < count; ++i) {
+          out[i] = decode_e4m3(encode_e4m3(uniform_pm2_keyed(key, first + i)));
+        }
+        return;
+      case Dtype::kF16:
+        for (std::size_t i = 0; i < count; ++i) {
+          out[i] = decode_f16(encode_f16(normal_keyed(key, first + i)));
+        }
+        return;
+      case Dtype::kBF16:
+        for (std::size_t i = 0; i < count; ++i) {
+          out[i] = decode_bf16(encode_bf16(normal_keyed(key, first + i)));
+        }
+        return;
+    }
+  }
+  for (std::size_t i = 0; i < count; ++i) {
+    out[i] = load_input(dtype, spec, rank, first + i);
+  }
+}
+
+// Float32 sums (rank order) of one block.
+inline void f32_sum_block(Dtype dtype, const InputSpec& spec, std::size_t first, std::size_t count, float* acc) {
+  float x[kBlock];
+  std::fill(acc, acc + count, 0.0f);
+  for (int r = 0; r < spec.ranks; ++r) {
+    load_block(dtype, spec, r, first, count, x);
+    for (std::size_t i = 0; i < count; ++i) {
+      acc[i] += x[i];
+    }
+  }
+}
+
+// Sequential sums with a rounding to the accumulator type after every add (the reference's model).
+inline void semantic_sum_block(Dtype dtype, const InputSpec& spec, std::size_t first, std::size_t count, float* acc) {
+  float x[kBlock];
+  std::fill(acc, acc + count, 0.0f);
+  for (int r = 0; r < spec.ranks; ++r) {
+    load_block(dtype, spec, r, first, count, x);
+    if (dtype == Dtype::kBF16) {
+      for (std::size_t i = 0; i < count; ++i) {
+        acc[i] = decode_bf16(encode_bf16(acc[i] + x[i]));
+      }
+    } else {
+      for (std::size_t i = 0; i < count; ++i) {
+        acc[i] = round_to_f16(acc[i] + x[i]);
+      }
+    }
+  }
+}
+
+// Both models of one block with a single pass over the generated inputs.
+inline void both_sums_block(Dtype dtype, const InputSpec& spec, std::size_t first, std::size_t count, float* sequential,
+                            float* sum32) {
+  float x[kBlock];
+  std::fill(sequential, sequential + count, 0.0f);
+  std::fill(sum32, sum32 + count, 0.0f);
+  for (int r = 0; r < spec.ranks; ++r) {
+    load_block(dtype, spec, r, first, count, x);
+    for (std::size_t i = 0; i < count; ++i) {
+      sum32[i] += x[i];
+      sequential[i] = dtype == Dtype::kBF16 ? decode_bf16(encode_bf16(sequential[i] + x[i])) : round_to_f16(sequential[i] + x[i]);
+    }
+  }
+}
+
 inline float semantic_sum(Dtype dtype, const InputSpec& spec, std::size_t element) {
   float acc = 0.0f;
   if (dtype == Dtype::kBF16) {
@@ -60,14 +164,6 @@ inline float semantic_sum(Dtype dtype, const InputSpec& spec, std::size_t elemen
     for (int r = 0; r < spec.ranks; ++r) {
       acc = round_to_f16(acc + load_input(dtype, spec, r, element));
     }
-  }
-  return acc;
-}
-
-inline float f32_sum(Dtype dtype, const InputSpec& spec, std::size_t element) {
-  float acc = 0.0f;
-  for (int r = 0; r < spec.ranks; ++r) {
-    acc += load_input(dtype, spec, r, element);
   }
   return acc;
 }
@@ -179,8 +275,13 @@ void generate_input(Dtype dtype, const InputSpec& spec, int rank, std::size_t fi
 void reduce_semantic(Dtype dtype, const InputSpec& spec, std::size_t first_element,
                      std::size_t element_count, void* out, int threads) {
   parallel_for(element_count, threads, [&](std::size_t b, std::size_t e, int) {
-    for (std::size_t i = b; i < e; ++i) {
-      store_cast(dtype, out, i, semantic_sum(dtype, spec, first_element + i));
+    float acc[kBlock];
+    for (std::size_t at = b; at < e; at += kBlock) {
+      const std::size_t count = std::min(kBlock, e - at);
+      semantic_sum_block(dtype, spec, first_element + at, count, acc);
+      for (std::size_t i = 0; i < count; ++i) {
+        store_cast(dtype, out, at + i, acc[i]);
+      }
     }
   });
 }
@@ -188,8 +289,8 @@ void reduce_semantic(Dtype dtype, const InputSpec& spec, std::size_t first_eleme
 void reduce_f32(Dtype dtype, const InputSpec& spec, std::size_t first_element,
                 std::size_t element_count, float* out, int threads) {
   parallel_for(element_count, threads, [&](std::size_t b, std::size_t e, int) {
-    for (std::size_t i = b; i < e; ++i) {
-      out[i] = f32_sum(dtype, spec, first_element + i);
+    for (std::size_t at = b; at < e; at += kBlock) {
+      f32_sum_block(dtype, spec, first_element + at, std::min(kBlock, e - at), out + at);
     }
   });
 }
@@ -197,8 +298,13 @@ void reduce_f32(Dtype dtype, const InputSpec& spec, std::size_t first_element,
 void reduce_f32_cast(Dtype dtype, const InputSpec& spec, std::size_t first_element,
                      std::size_t element_count, void* out, int threads) {
   parallel_for(element_count, threads, [&](std::size_t b, std::size_t e, int) {
-    for (std::size_t i = b; i < e; ++i) {
-      store_cast(dtype, out, i, f32_sum(dtype, spec, first_element + i));
+    float acc[kBlock];
+    for (std::size_t at = b; at < e; at += kBlock) {
+      const std::size_t count = std::min(kBlock, e - at);
+      f32_sum_block(dtype, spec, first_element + at, count, acc);
+      for (std::size_t i = 0; i < count; ++i) {
+        store_cast(dtype, out, at + i, acc[i]);
+      }
     }
   });
 }
@@ -218,9 +324,14 @@ PrecisionMetrics compare(Dtype dtype, const InputSpec& spec, const void* result,
   std::vector<Partial> partials(static_cast<std::size_t>(threads));
   parallel_for(element_count, threads, [&](std::size_t b, std::size_t e, int w) {
     Partial p;
+    float sequential_block[kBlock];
+    float sum32_block[kBlock];
     for (std::size_t i = b; i < e; ++i) {
+      if ((i - b) % kBlock == 0) {
+        both_sums_block(dtype, spec, i, std::min(kBlock, e - i), sequential_block, sum32_block);
+      }
       const uint32_t got = load_code(dtype, result, i);
-      const float sequential = semantic_sum(dtype, spec, i);
+      const float sequential = sequential_block[(i - b) % kBlock];
       const uint32_t want_semantic = encode_code(dtype, sequential);
       // In-switch FP8: the value just below or just above the sum is accepted; a sum that is
       // representable must come back as itself; beyond +-448 the switch may answer NaN.
@@ -238,7 +349,7 @@ PrecisionMetrics compare(Dtype dtype, const InputSpec& spec, const void* result,
         }
       }
       p.switch_model += !switch_ok;
-      const float sum32 = f32_sum(dtype, spec, i);
+      const float sum32 = sum32_block[(i - b) % kBlock];
       const uint32_t want_requant = encode_code(dtype, sum32);
       p.exact += got != want_semantic;
       p.requant += got != want_requant;
