@@ -1,22 +1,24 @@
 // Fused row-parallel block-scaled FP8 GEMM + all-reduce for sm_100a.
 //
-// One persistent CTA per SM, warp-specialised:
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and W tiles (128 x 128 bytes
-//               each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
-//   warps 1, 3  MMA issuers (alternate K blocks): tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per stage) into one of
-//               four TMEM accumulators; tcgen05.commit hands the stage back and the accumulator on
-//   warps 2-9   promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
-//               tcgen05.ld of the 128-deep partial product, multiply by
-//               a_scale[row, kblock] * w_scale[ntile, kblock], accumulate in float32 registers
-//               (the float block scales are not the hardware's UE8M0 1x32 format, so the scaling
-//               cannot be left to the tensor core); after the last K block the BF16 row is stored
-//               to this rank's copy of the symmetric output and the tile's arrival is counted
-//               at the tile's owner with one release-add over NVLink
-//   warp 14     (several ranks) waits for the epilogue's tile stores and publishes the tile
-//   warps 10-13 reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
-//               wait until every rank has published the tile, then multimem.ld_reduce (float32
-//               accumulation in the switch) + multimem.st the tile in place, so that the sum
-//               lands in every rank's copy while other tiles are still being multiplied
+// One persistent CTA per SM, 16 warps, warp-specialised:
+//   warp 0       TMA producer: cp.async.bulk.tensor loads of the A and W tiles (128 x 128 bytes
+//                each, 128-byte swizzle) into a ring of shared-memory stages (plain per-CTA loads)
+//   warps 1, 3   MMA issuers, alternate K blocks: tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per
+//                stage) into one of four TMEM accumulators; one tcgen05.commit per K block hands
+//                the stage back to the producer and the accumulator on to the promotion warps
+//   warp 2       publisher (several ranks): waits for the promotion warps' tile stores and counts
+//                the tile's arrival at the tile's owner with one release-add over NVLink, so that
+//                no promotion thread waits for its own stores to drain
+//   warps 4-11   promotion + epilogue (two warps per TMEM lane quarter, 64 columns each):
+//                tcgen05.ld of the 128-deep partial product, multiply by
+//                a_scale[row, kblock] * w_scale[ntile, kblock], accumulate in float32 registers
+//                (the float block scales are not the hardware's UE8M0 1x32 format, so the scaling
+//                cannot be left to the tensor core); after the last K block the BF16 row is stored
+//                to this rank's copy of the symmetric output
+//   warps 12-15  reducers (on the first `reducer_ctas` CTAs): for the output tiles this rank owns,
+//                wait until every rank has published the tile, then multimem.ld_reduce (float32
+//                accumulation in the switch) + multimem.st the tile in place, so that the sum
+//                lands in every rank's copy while other tiles are still being multiplied
 // Every wait (mbarrier, flag, cross-GPU barrier) is bounded; on expiry the kernel records a
 // status bit, stops waiting, releases its TMEM and returns.
 #include <cuda.h>
