@@ -44,3 +44,4 @@ def test_cmake_build_and_ctest(tmp_path):
         assert "arch=compute_100a,code=sm_100a" in text and "compute_52" not in text and "sm_90" not in text
     tests = subprocess.run(["ctest", "--test-dir", str(build), "--output-on-failure"], capture_output=True, text=True, timeout=600)
     assert tests.returncode == 0 and "100% tests passed" in tests.stdout, tests.stdout + tests.stderr
+    assert "c_api_from_plain_c" in tests.stdout  # the plain-C example is one of them
