@@ -15,6 +15,7 @@
 #include "msharp/config.h"
 #include "msharp/fake_driver.h"
 #include "msharp/gemm_allreduce.h"
+#include "msharp/host_emulation.h"
 #include "msharp/json.h"
 #include "msharp/kernels.h"
 #include "msharp/oracle.h"
@@ -656,6 +657,13 @@ int msharp_allreduce_pull(void* comm, void* symm, int dtype, int acc_f32, size_t
     auto* h = static_cast<CommHandle*>(comm);
     const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
     check_range(m, offset, bytes);
+    if (h->api->is_fake) {  // driver stand-in: the collective is played through on the CPU
+      msharp::validate_pull_launch(reinterpret_cast<const void*>(m.output_ptr(m.rank()) + offset), bytes,
+                                   msharp::LaunchShape{grid, block, unroll});
+      msharp::emulate_allreduce(*h->bootstrap, m, to_dtype(dtype), m.output_offset + offset, m.output_offset + offset, bytes,
+                                nullptr, 1.0f);
+      return;
+    }
     void* target;
     if (m.world() == 1) {
       target = reinterpret_cast<void*>(m.output_ptr(0) + offset);
@@ -677,6 +685,11 @@ int msharp_allreduce_sw_f32(void* comm, void* symm, size_t offset, size_t bytes,
     auto* h = static_cast<CommHandle*>(comm);
     const msharp::SymmetricMemory& m = *static_cast<SymmHandle*>(symm)->mem;
     check_range(m, offset, bytes);
+    if (h->api->is_fake) {  // with the stand-in `in_scales_device` is a host pointer
+      msharp::emulate_allreduce(*h->bootstrap, m, msharp::Dtype::kE4M3, m.output_offset + offset, m.output_offset + offset,
+                                bytes, reinterpret_cast<const float*>(in_scales_device), out_scale_inv);
+      return;
+    }
     void* mc = m.mc_base != 0 ? reinterpret_cast<void*>(m.mc_output_ptr() + offset) : nullptr;
     msharp::LaunchShape shape{grid, block, 0};
     msharp::launch_allreduce_sw_f32(h->ctx->device(), outputs_of(m, offset), mc, bytes,
@@ -693,6 +706,17 @@ int msharp_allreduce_bulk_push(void* comm, void* symm, int dtype, size_t offset,
     check_range(m, offset, bytes);
     if (m.input_offset == m.output_offset) {
       throw std::runtime_error("bulk push is out of place: allocate the buffer with the input/output layout");
+    }
+    if (h->api->is_fake) {
+      if (bytes % 16 != 0) {
+        throw std::runtime_error("bulk all-reduce: size must be a multiple of 16 bytes");
+      }
+      if (to_dtype(dtype) == msharp::Dtype::kE4M3) {
+        throw std::runtime_error("bulk all-reduce: the memory-side add has no FP8 form");
+      }
+      msharp::emulate_allreduce(*h->bootstrap, m, to_dtype(dtype), m.input_offset + offset, m.output_offset + offset, bytes,
+                                nullptr, 1.0f);
+      return;
     }
     msharp::LaunchShape shape{grid, 0, 0};
     msharp::launch_allreduce_bulk_push(h->ctx->device(), to_dtype(dtype),
@@ -718,8 +742,8 @@ int msharp_bulk_multimem_compiled(void) { return msharp::bulk_multimem_compiled(
 int msharp_gemm_workspace_init(void* comm) {
   return guarded([&] {
     auto* h = static_cast<CommHandle*>(comm);
-    if (h->gemm_ws) {
-      return;
+    if (h->gemm_ws || h->api->is_fake) {
+      return;  // the emulation needs no tile flags
     }
     msharp::SymmOptions opt = h->base;
     opt.payload_bytes = msharp::kGemmWsBytes;
@@ -751,6 +775,18 @@ int msharp_gemm_allreduce(void* comm, void* out_symm, uint64_t a, uint64_t a_sca
     args.out_local = reinterpret_cast<void*>(out.output_ptr(out.rank()));
     args.reducer_ctas = reducer_ctas & 0xffff;
     args.tile_n = (reducer_ctas >> 16) & 0xffff;  // optional tile width (128 / 256) in the upper half
+    if (h->api->is_fake) {
+      // Driver stand-in: operands are host pointers. Same argument rules as the kernel, then this
+      // rank's product on the CPU into its own copy of the output and the emulated BF16 all-reduce.
+      msharp::validate_gemm_allreduce_args(args, out.world(), false);
+      msharp::emulate_gemm_partial_bf16(static_cast<const uint8_t*>(args.a), args.a_scales, static_cast<const uint8_t*>(args.w),
+                                        args.w_scales, m, n, k, static_cast<uint16_t*>(args.out_local));
+      if (out.world() > 1) {
+        msharp::emulate_allreduce(*h->bootstrap, out, msharp::Dtype::kBF16, out.output_offset, out.output_offset,
+                                  static_cast<std::size_t>(m) * static_cast<std::size_t>(n) * 2, nullptr, 1.0f);
+      }
+      return;
+    }
     uint64_t peers[msharp::kMaxWorld] = {0};
     if (out.world() > 1) {
       if (out.mc_base == 0) {

@@ -28,6 +28,7 @@
 #include <vector>
 
 #include "msharp/comm_context.h"
+#include "msharp/host_emulation.h"
 #include "msharp/json.h"
 #include "msharp/kernels.h"
 #include "msharp/numerics.h"
@@ -135,12 +136,11 @@ void canary_smoke_test(RankRun& run) {
 }
 
 // ---- host emulation (driver stand-in only) ---------------------------------------------------
-// With the host-memory stand-in the "device" pointers are ordinary host pointers into memory that
-// all rank processes share, so the collective can be played through on the CPU: same slicing as
-// the kernels (rank r reduces the r-th part and writes it into every replica), float32 sum in rank
-// order and one final cast (what the sw_f32 kernel computes and what the oracle calls the float32
-// model). It exists to run the whole benchmark flow (iterations, hashes, check, report, exit code)
-// among CPU processes, on one machine or through the multi-host launch path; it measures nothing.
+// With the host-memory stand-in the collective is played through on the CPU (host_emulation.h):
+// same slicing as the kernels, float32 sum in rank order and one final cast (what the sw_f32
+// kernel computes and what the oracle calls the float32 model). It exists to run the whole
+// benchmark flow (iterations, hashes, check, report, exit code) among CPU processes, on one
+// machine or through the multi-host launch path; it measures nothing.
 void emulate_initialize(RankRun& run) {
   const Config& cfg = run.cfg;
   InputSpec spec;
@@ -156,30 +156,7 @@ void emulate_initialize(RankRun& run) {
 
 void emulate_collective(RankRun& run) {
   const Config& cfg = run.cfg;
-  const int world = run.rank.world_size;
-  const std::size_t size = dtype_size(run.dtype);
-  const std::size_t elements = cfg.bytes / size;
-  const std::size_t per_rank = (elements + static_cast<std::size_t>(world) - 1) / static_cast<std::size_t>(world);
-  const std::size_t begin = std::min(elements, per_rank * static_cast<std::size_t>(run.rank.world_rank));
-  const std::size_t end = std::min(elements, begin + per_rank);
-  run.comm.barrier();  // the opening barrier of the kernels: every rank's input is in place
-  if (end > begin) {
-    std::vector<const void*> inputs(static_cast<std::size_t>(world));
-    for (int r = 0; r < world; ++r) {
-      inputs[static_cast<std::size_t>(r)] = reinterpret_cast<const unsigned char*>(run.mem->input_ptr(r)) + begin * size;
-    }
-    std::vector<float> sums(end - begin);
-    reduce_arrays_f32(run.dtype, inputs.data(), world, end - begin, sums.data());
-    std::vector<unsigned char> slice((end - begin) * size);
-    cast_from_f32(run.dtype, sums.data(), end - begin, slice.data());
-    run.comm.barrier();  // in place: nobody overwrites a slice that a peer still reads
-    for (int r = 0; r < world; ++r) {
-      std::memcpy(reinterpret_cast<unsigned char*>(run.mem->output_ptr(r)) + begin * size, slice.data(), slice.size());
-    }
-  } else {
-    run.comm.barrier();
-  }
-  run.comm.barrier();  // the closing barrier: every slice has landed in every replica
+  emulate_allreduce(run.comm, *run.mem, run.dtype, run.mem->input_offset, run.mem->output_offset, cfg.bytes, nullptr, 1.0f);
   // Host-side fault injection for tests of the failure path: MSHARP_FAKE_CORRUPT="rank:byte" makes
   // that rank flip one bit of its own replica, as a lost or torn store would.
   if (const char* spec = std::getenv("MSHARP_FAKE_CORRUPT"); spec != nullptr && *spec != '\0') {

@@ -53,4 +53,9 @@ struct GemmAllReduceArgs {
 void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const GemmAllReduceArgs& args,
                            cudaStream_t stream);
 
+// The argument rules of launch_gemm_allreduce by themselves (shape multiples, alignment, tile count,
+// tile width, and for several ranks the multicast alias and workspace unless `needs_workspace` is
+// false); throws std::runtime_error. Returns the tile width that will be used (128 or 256).
+int validate_gemm_allreduce_args(const GemmAllReduceArgs& args, int world, bool needs_workspace = true);
+
 }  // namespace msharp

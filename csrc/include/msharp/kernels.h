@@ -51,6 +51,9 @@ enum class PullAcc : int { kNative = 0, kF32 = 1 };
 // one rank pass the local pointer (a plain copy pass is run in its place).
 void launch_allreduce_pull(const DeviceComm& comm, Dtype dtype, PullAcc acc, void* mc_data, std::size_t bytes,
                            const LaunchShape& shape, cudaStream_t stream);
+// The argument rules of launch_allreduce_pull by themselves (16-byte aligned non-null buffer, size a
+// nonzero multiple of 4, unroll 1 / 2 / 4 / 8 / 16 or 0, block a multiple of 32 up to 1024); throws.
+void validate_pull_launch(const void* data, std::size_t bytes, const LaunchShape& shape);
 // The reference's launch shape: one rank, <=4096x256 threads, one 4-byte ld_reduce + st per
 // step, no device barrier (the caller brackets it with host barriers). For comparisons only.
 void launch_allreduce_reference_geometry(Dtype dtype, void* mc_data, std::size_t bytes, cudaStream_t stream);

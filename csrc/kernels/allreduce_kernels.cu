@@ -489,9 +489,20 @@ int pull_kind(Dtype dtype, PullAcc acc) {
 
 }  // namespace
 
+void validate_pull_launch(const void* data, std::size_t bytes, const LaunchShape& shape) {
+  validate_buffer(data, bytes, "pull all-reduce");
+  const int u = shape.unroll;
+  if (u != 0 && u != 1 && u != 2 && u != 4 && u != 8 && u != 16) {
+    throw std::runtime_error("pull all-reduce: unroll must be 1, 2, 4, 8 or 16");
+  }
+  if (shape.grid < 0 || shape.block < 0 || shape.block > 1024 || shape.block % 32 != 0) {
+    throw std::runtime_error("pull all-reduce: block must be a multiple of 32 up to 1024 and grid non-negative");
+  }
+}
+
 void launch_allreduce_pull(const DeviceComm& comm, Dtype dtype, PullAcc acc, void* mc_data, std::size_t bytes,
                            const LaunchShape& shape, cudaStream_t stream) {
-  validate_buffer(mc_data, bytes, "pull all-reduce");
+  validate_pull_launch(mc_data, bytes, shape);
   if (comm.world == 1) {
     launch_pull_kind<dev::kReduceLocalCopy>(comm, mc_data, bytes, shape, stream);
     return;

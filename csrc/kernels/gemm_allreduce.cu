@@ -552,7 +552,7 @@ CUtensorMap make_tile_map(const DriverApi& api, const void* base, int rows, int 
 
 }  // namespace
 
-void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const GemmAllReduceArgs& a, cudaStream_t stream) {
+int validate_gemm_allreduce_args(const GemmAllReduceArgs& a, int world, bool needs_workspace) {
   auto aligned = [](const void* ptr) { return ptr != nullptr && reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.m % BM != 0 || a.n % BN != 0 || a.k % BK != 0) {
     throw std::runtime_error("gemm_allreduce: M and N must be positive multiples of 128 and K a positive multiple of 128");
@@ -564,10 +564,25 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
   if (tiles > kGemmMaxTiles) {
     throw std::runtime_error("gemm_allreduce: more than " + std::to_string(kGemmMaxTiles) + " output tiles");
   }
-  const bool multi = comm.world > 1;
-  if (multi && (a.out_mc == nullptr || a.ws_local == nullptr)) {
+  if (world > 1 && needs_workspace && (a.out_mc == nullptr || a.ws_local == nullptr)) {
     throw std::runtime_error("gemm_allreduce: several ranks need the multicast alias of the output and a workspace");
   }
+  // 128-wide tiles are the default: measured on B200 at 8192 x 8192 x 3584 they take 0.42 ms against
+  // 0.78 ms for 256-wide tiles (two accumulators instead of four, twice the promotion work per
+  // thread); the wide tile stays selectable for shapes where it may pay.
+  int tile_n = 128;
+  if (a.tile_n == 128 || a.tile_n == 256) {
+    tile_n = a.tile_n;
+  }
+  if (a.n % tile_n != 0) {
+    throw std::runtime_error("gemm_allreduce: N is not a multiple of the requested tile width");
+  }
+  return tile_n;
+}
+
+void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const GemmAllReduceArgs& a, cudaStream_t stream) {
+  const int tile_n = validate_gemm_allreduce_args(a, comm.world);
+  const bool multi = comm.world > 1;
   GemmParams p{};
   p.a_scales = a.a_scales;
   p.w_scales = a.w_scales;
@@ -582,16 +597,6 @@ void launch_gemm_allreduce(const DriverApi& api, const DeviceComm& comm, const G
     if (multi && p.ws_peers.ptr[r] == 0) {
       throw std::runtime_error("gemm_allreduce: workspace address of rank " + std::to_string(r) + " is missing");
     }
-  }
-  // 128-wide tiles are the default: measured on B200 at 8192 x 8192 x 3584 they take 0.42 ms against
-  // 0.78 ms for 256-wide tiles (two accumulators instead of four, twice the promotion work per
-  // thread); the wide tile stays selectable for shapes where it may pay.
-  int tile_n = 128;
-  if (a.tile_n == 128 || a.tile_n == 256) {
-    tile_n = a.tile_n;
-  }
-  if (a.n % tile_n != 0) {
-    throw std::runtime_error("gemm_allreduce: N is not a multiple of the requested tile width");
   }
   const int sms = device_sm_count();
   // The grid is always one CTA per SM so that the reducer CTAs (which wait for their peers) are

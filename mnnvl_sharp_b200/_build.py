@@ -43,7 +43,7 @@ INCLUDES = ["-I", str(CSRC / "include"), "-I", str(CSRC / "kernels"), "-I", str(
 LIB_SOURCES = [
     "core/oracle.cc", "core/config.cc", "core/json.cc", "core/yaml_lite.cc", "core/rack.cc", "core/report.cc",
     "comm/bootstrap.cc", "comm/spawn.cc",
-    "mem/driver_api.cc", "mem/fake_driver.cc", "mem/topology.cc", "mem/symm_mem.cc", "mem/comm_context.cc",
+    "mem/driver_api.cc", "mem/fake_driver.cc", "mem/topology.cc", "mem/symm_mem.cc", "mem/comm_context.cc", "mem/host_emulation.cc",
     "kernels/util_kernels.cu", "kernels/allreduce_kernels.cu",
     "app/runner.cc", "app/c_api.cc",
 ]

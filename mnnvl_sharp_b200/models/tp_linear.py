@@ -30,9 +30,10 @@ class RowParallelLinearFP8(torch.nn.Module):
         self.out_features = out_features
         self.k_local = in_features // comm.world
         self.max_tokens = max_tokens
+        device = "cpu" if comm.fake else "cuda"  # CPU only on the host-memory driver stand-in
         if weight is None:
-            g = torch.Generator(device="cuda").manual_seed(seed)  # same full weight on every rank, then sliced
-            weight = torch.randn(out_features, in_features, device="cuda", generator=g) / in_features ** 0.5
+            g = torch.Generator(device=device).manual_seed(seed)  # same full weight on every rank, then sliced
+            weight = torch.randn(out_features, in_features, device=device, generator=g) / in_features ** 0.5
         local = weight[:, comm.rank * self.k_local:(comm.rank + 1) * self.k_local].contiguous()
         q, s = quantize_blockwise(local, BLOCK)
         self.register_buffer("weight_fp8", q)
@@ -94,9 +95,10 @@ class TensorParallelFFN(torch.nn.Module):
         self.comm = comm
         self.hidden = hidden
         self.local_cols = intermediate // comm.world
-        g = torch.Generator(device="cuda").manual_seed(seed + 1)  # full weights on every rank, then sliced
-        gate = torch.randn(intermediate, hidden, device="cuda", generator=g) / hidden ** 0.5
-        up = torch.randn(intermediate, hidden, device="cuda", generator=g) / hidden ** 0.5
+        device = "cpu" if comm.fake else "cuda"
+        g = torch.Generator(device=device).manual_seed(seed + 1)  # full weights on every rank, then sliced
+        gate = torch.randn(intermediate, hidden, device=device, generator=g) / hidden ** 0.5
+        up = torch.randn(intermediate, hidden, device=device, generator=g) / hidden ** 0.5
         rows = slice(comm.rank * self.local_cols, (comm.rank + 1) * self.local_cols)
         self.register_buffer("gate_weight", gate[rows].to(torch.bfloat16).contiguous())
         self.register_buffer("up_weight", up[rows].to(torch.bfloat16).contiguous())

@@ -16,7 +16,11 @@ from .. import _native as N
 from ..parallel.symmetric import Communicator, SymmetricBuffer
 
 
-def _stream() -> int:
+def _stream(comm: Communicator | None = None) -> int:
+    """The current CUDA stream; 0 for a communicator on the host-memory driver stand-in, where the
+    native library plays the collective through on the CPU and no stream exists."""
+    if comm is not None and comm.fake:
+        return 0
     return int(torch.cuda.current_stream().cuda_stream)
 
 
@@ -27,7 +31,7 @@ def all_reduce_pull(comm: Communicator, buf: SymmetricBuffer, dtype: str, nbytes
     if acc_f32 is None:
         acc_f32 = dtype != "e4m3"
     N.check(N.lib.msharp_allreduce_pull(comm.handle, buf.handle, N.DTYPES[dtype], 1 if acc_f32 else 0, offset,
-                                        buf.payload_bytes if nbytes is None else nbytes, grid, block, unroll, _stream()))
+                                        buf.payload_bytes if nbytes is None else nbytes, grid, block, unroll, _stream(comm)))
 
 
 def all_reduce_sw_f32(comm: Communicator, buf: SymmetricBuffer, nbytes: int | None = None, offset: int = 0,
@@ -37,18 +41,19 @@ def all_reduce_sw_f32(comm: Communicator, buf: SymmetricBuffer, nbytes: int | No
     rank order. `in_scales` is a float32 CUDA tensor with one scale per rank (default all 1)."""
     scales_ptr = 0
     if in_scales is not None:
-        if in_scales.dtype != torch.float32 or not in_scales.is_cuda or in_scales.numel() < comm.world:
-            raise ValueError("in_scales must be a float32 CUDA tensor with one entry per rank")
+        if in_scales.dtype != torch.float32 or in_scales.is_cuda == comm.fake or in_scales.numel() < comm.world:
+            raise ValueError("in_scales must be a float32 CUDA tensor with one entry per rank "
+                             "(a CPU tensor on the host-memory driver stand-in)")
         scales_ptr = in_scales.data_ptr()
     N.check(N.lib.msharp_allreduce_sw_f32(comm.handle, buf.handle, offset, buf.payload_bytes if nbytes is None else nbytes,
-                                          scales_ptr, 1.0 / out_scale, grid, block, _stream()))
+                                          scales_ptr, 1.0 / out_scale, grid, block, _stream(comm)))
 
 
 def all_reduce_bulk_push(comm: Communicator, buf: SymmetricBuffer, dtype: str = "f16", nbytes: int | None = None,
                          offset: int = 0, grid: int = 0) -> None:
     """Out of place (input region -> output region of an 'input_output' buffer), F16 or BF16."""
     N.check(N.lib.msharp_allreduce_bulk_push(comm.handle, buf.handle, N.DTYPES[dtype], offset,
-                                             buf.payload_bytes if nbytes is None else nbytes, grid, _stream()))
+                                             buf.payload_bytes if nbytes is None else nbytes, grid, _stream(comm)))
 
 
 def all_reduce_reference_geometry(buf: SymmetricBuffer, dtype: str, nbytes: int) -> None:
@@ -89,12 +94,26 @@ def all_reduce(comm: Communicator, buf: SymmetricBuffer, dtype: str, backend: st
 
 def init_pattern(buf: SymmetricBuffer, dtype: str, pattern: str, rank: int, nbytes: int, seed: int = 2025,
                  region: str = "input") -> None:
+    if buf.comm.fake:  # driver stand-in: generate on the host and copy in
+        from ..utils import numerics as nm
+
+        buf.write(nm.generate(dtype, pattern, rank, nbytes // nm.element_size(dtype), seed=seed), region=region)
+        return
     ptr = buf.input_ptr() if region == "input" else buf.output_ptr()
     N.check(N.lib.msharp_init_pattern(N.DTYPES[dtype], N.PATTERNS[pattern], seed, rank, ptr, nbytes, _stream()))
 
 
 def poison_fill(ptr: int, nbytes: int) -> None:
     N.check(N.lib.msharp_poison_fill(ptr, nbytes, _stream()))
+
+
+def replica_hash(buf: SymmetricBuffer, nbytes: int) -> int:
+    """Hash of the first `nbytes` of this rank's output region (equal on all ranks after an all-reduce)."""
+    if buf.comm.fake:
+        from ..utils import numerics as nm
+
+        return nm.hash_words(buf.read(nbytes))
+    return device_hash(buf.output_ptr(), nbytes)
 
 
 def device_hash(ptr: int, nbytes: int) -> int:

@@ -54,11 +54,12 @@ class GemmAllReduce:
             raise ValueError("shape mismatch: A [M, K], W [N, K] with K a multiple of 128")
         for t, shape, dt in ((a, (m, k), torch.float8_e4m3fn), (w, (n, k), torch.float8_e4m3fn),
                              (a_scales, (m, k // BLOCK), torch.float32), (w_scales, (n // BLOCK, k // BLOCK), torch.float32)):
-            if tuple(t.shape) != shape or t.dtype != dt or not t.is_cuda or not t.is_contiguous():
+            # on the host-memory driver stand-in the operands are CPU tensors and the product runs on the CPU
+            if tuple(t.shape) != shape or t.dtype != dt or t.is_cuda == self.comm.fake or not t.is_contiguous():
                 raise ValueError(f"expected a contiguous CUDA tensor of shape {shape} and dtype {dt}")
+        stream = 0 if self.comm.fake else int(torch.cuda.current_stream().cuda_stream)
         N.check(N.lib.msharp_gemm_allreduce(self.comm.handle, self.out_buf.handle, a.data_ptr(), a_scales.data_ptr(),
-                                            w.data_ptr(), w_scales.data_ptr(), m, n, k, reducer_ctas,
-                                            int(torch.cuda.current_stream().cuda_stream)))
+                                            w.data_ptr(), w_scales.data_ptr(), m, n, k, reducer_ctas, stream))
         return self.out
 
     def free(self) -> None:

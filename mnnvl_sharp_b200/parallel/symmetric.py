@@ -168,10 +168,13 @@ class SymmetricBuffer:
 
     def tensor(self, dtype, region: str = "output", rank: int | None = None, nbytes: int | None = None):
         """A torch tensor viewing this buffer's memory on `rank` (default: own) without a copy."""
-        from .tensor_view import device_tensor
+        from .tensor_view import device_tensor, host_tensor
 
         ptr = self.output_ptr(rank) if region == "output" else self.input_ptr(rank)
-        return device_tensor(ptr, self.payload_bytes if nbytes is None else nbytes, dtype, self.comm.device, owner=self)
+        size = self.payload_bytes if nbytes is None else nbytes
+        if self.comm.fake:
+            return host_tensor(ptr, size, dtype, owner=self)
+        return device_tensor(ptr, size, dtype, self.comm.device, owner=self)
 
     def free(self) -> None:
         """Collective."""

@@ -21,3 +21,14 @@ class _CudaArray:
 def device_tensor(ptr: int, nbytes: int, dtype: torch.dtype, device: int, owner=None) -> torch.Tensor:
     raw = torch.as_tensor(_CudaArray(ptr, nbytes, owner), device=torch.device("cuda", device))
     return raw.view(dtype)
+
+
+def host_tensor(ptr: int, nbytes: int, dtype: torch.dtype, owner=None) -> torch.Tensor:
+    """The same for communicators on the host-memory driver stand-in, whose "device" pointers are
+    host pointers: a CPU tensor over that memory, without a copy."""
+    import ctypes
+
+    array = (ctypes.c_uint8 * nbytes).from_address(ptr)
+    raw = torch.frombuffer(array, dtype=torch.uint8)
+    raw._msharp_owner = owner  # keeps the allocation alive as long as this tensor object
+    return raw.view(dtype)

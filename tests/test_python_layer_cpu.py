@@ -1,0 +1,229 @@
+"""The Python operators and layers among CPU processes, on the host-memory driver stand-in.
+
+Each rank is a real process with a real control plane and really shared symmetric buffers; only
+the kernels are replaced by the native library's CPU emulation of the same collectives (float32
+sum in rank order, one final cast; rank r reduces the r-th part into every copy). What is tested
+is everything the kernels do not do: argument plumbing of `ops.all_reduce*` (offsets, sub-ranges,
+scales, layouts, automatic backend choice), zero-copy tensor views, the data-parallel gradient
+averager and the tensor-parallel layers' sharding, quantisation and result layout.
+"""
+import multiprocessing as mp
+import os
+import time
+
+import numpy as np
+import pytest
+
+CTX = mp.get_context("spawn")
+
+
+def run_ranks(target, world, *args, timeout=120):
+    session = f"py{os.getpid()}_{time.monotonic_ns()}"
+    q = CTX.Queue()
+    procs = [CTX.Process(target=_entry, args=(target, r, world, session, q) + args) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    deadline = time.time() + timeout
+    while len(results) < world and time.time() < deadline:
+        try:
+            rank, value = q.get(timeout=0.5)
+            results[rank] = value
+        except Exception:
+            if all(not p.is_alive() for p in procs) and q.empty():
+                break
+    for p in procs:
+        p.join(timeout=10)
+        if p.is_alive():
+            p.kill()
+    assert sorted(results) == list(range(world)), results
+    for value in results.values():
+        assert not isinstance(value, str), value
+    return results
+
+
+def _entry(target, rank, world, session, q, *args):
+    import traceback
+
+    from mnnvl_sharp_b200 import _native as N
+    from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+
+    try:
+        N.lib.msharp_fake_driver_reset(8)
+        with Bootstrap(rank, world, session, timeout_ms=30000) as boot:
+            comm = Communicator(boot, rank % 8, fake_driver=True)
+            value = target(comm, boot, *args)
+            boot.barrier()
+            comm.close()
+        q.put((rank, value))
+    except Exception:  # noqa: BLE001
+        q.put((rank, traceback.format_exc()))
+
+
+# ------------------------------------------------------------------------------------ all-reduce
+def _all_reduce_cases(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+    from mnnvl_sharp_b200.utils import numerics as nm
+
+    out = {}
+    world = comm.world
+    # in-place backends over the whole buffer, sizes with a tail that is not a multiple of 16
+    for backend, dtype, nbytes in [("legacy", "e4m3", 4096 + 20), ("pull", "f16", 65536 + 4), ("pull", "bf16", 1 << 20),
+                                   ("sw_f32", "e4m3", 8192), ("auto", "f16", 32768)]:
+        buf = comm.alloc(nbytes)
+        ops.init_pattern(buf, dtype, "seeded", comm.rank, nbytes)
+        ops.all_reduce(comm, buf, dtype, backend=backend)
+        m = nm.compare(dtype, "seeded", world, buf.read(nbytes).view(nm.storage_dtype(dtype)))
+        hashes = boot.allgather_array(np.array([ops.replica_hash(buf, nbytes)], dtype=np.uint64))[:, 0]
+        out[f"{backend}/{dtype}"] = (m.requantized_mismatches, len(set(int(h) for h in hashes)))
+        buf.free()
+
+    # out of place (bulk push): the input region is left alone, the output region gets the sum
+    nbytes = 1 << 16
+    both = comm.alloc(nbytes, layout="input_output", multicast=False)
+    ops.init_pattern(both, "f16", "tagged", comm.rank, nbytes)
+    before = both.read(nbytes, region="input").copy()
+    assert ops.pick_backend(comm, both, "f16") == ("pull" if world == 1 else "tma_async")
+    ops.all_reduce(comm, both, "f16", backend="tma_async")
+    m = nm.compare("f16", "tagged", world, both.read(nbytes).view(np.uint16))
+    out["tma_async/f16"] = (m.exact_mismatches, bool((both.read(nbytes, region="input") == before).all()))
+    both.free()
+
+    # a sub-range: only [offset, offset + n) changes
+    buf = comm.alloc(1 << 16)
+    x = buf.tensor(torch.float16)
+    x.fill_(float(comm.rank + 1))
+    boot.barrier()
+    ops.all_reduce_pull(comm, buf, "f16", nbytes=4096, offset=8192)
+    total = world * (world + 1) / 2
+    inside = bool((x[4096:6144] == total).all())
+    outside = bool((x[:4096] == comm.rank + 1).all() and (x[6144:] == comm.rank + 1).all())
+    out["subrange"] = (inside, outside)
+    del x
+    buf.free()
+
+    # FP8 with per-rank input scales and an output scale: out = sat(sum_r s_r * x_r / out_scale)
+    buf = comm.alloc(4096)
+    codes = nm.encode("e4m3", np.full(4096, 0.5 * (comm.rank + 1), dtype=np.float32))
+    buf.write(codes)
+    scales = torch.tensor([2.0 ** -r for r in range(world)], dtype=torch.float32)
+    boot.barrier()
+    ops.all_reduce_sw_f32(comm, buf, in_scales=scales, out_scale=0.5)
+    want = sum(2.0 ** -r * 0.5 * (r + 1) for r in range(world)) / 0.5
+    got = nm.decode("e4m3", buf.read(4096))
+    out["scaled"] = (float(got[0]), float(nm.decode("e4m3", nm.encode("e4m3", np.array([want], dtype=np.float32)))[0]),
+                     bool((got == got[0]).all()))
+    buf.free()
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_all_reduce_operators(world):
+    for r in run_ranks(_all_reduce_cases, world).values():
+        for key in ("legacy/e4m3", "pull/f16", "pull/bf16", "sw_f32/e4m3", "auto/f16"):
+            assert r[key] == (0, 1), (key, r[key])  # equals cast(float32 sum); all replicas identical
+        assert r["tma_async/f16"] == (0, True)
+        assert r["subrange"] == (True, True)
+        assert r["scaled"][0] == r["scaled"][1] and r["scaled"][2]
+
+
+def _refusals(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    buf = comm.alloc(4096)
+    seen = []
+    for call in (lambda: ops.all_reduce(comm, buf, "f16", backend="legacy"),
+                 lambda: ops.all_reduce(comm, buf, "f16", backend="sw_f32"),
+                 lambda: ops.all_reduce(comm, buf, "f16", backend="ring"),
+                 lambda: ops.all_reduce(comm, buf, "f16", backend="tma_async"),  # needs the two-region layout
+                 lambda: ops.all_reduce_sw_f32(comm, buf, in_scales=torch.ones(comm.world, dtype=torch.float64)),
+                 lambda: ops.all_reduce_pull(comm, buf, "f16", nbytes=8192)):
+        try:
+            call()
+            seen.append("accepted")
+        except Exception as ex:  # noqa: BLE001
+            seen.append(type(ex).__name__)
+    boot.barrier()
+    buf.free()
+    return seen
+
+
+def test_operator_argument_errors_are_raised_on_every_rank_before_any_collective_step():
+    for seen in run_ranks(_refusals, 2).values():
+        assert seen == ["ValueError", "ValueError", "ValueError", "NativeError", "ValueError", "NativeError"]
+
+
+# ------------------------------------------------------------------------------------ layers
+def _gradient_averaging(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200.models import GradientAllReducer
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(24, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4, bias=False))
+    model[2].weight.requires_grad_(comm.rank >= 0)
+    for i, p in enumerate(model.parameters()):
+        p.grad = torch.full_like(p, float(comm.rank + 1) * (i + 1))
+    model[0].bias.grad = None  # a parameter without a gradient on this step contributes zeros
+    reducer = GradientAllReducer(comm, model.parameters())
+    boot.barrier()
+    reducer.step()
+    mean = (comm.world + 1) / 2.0
+    ok = all(p.grad is None or torch.allclose(p.grad, torch.full_like(p, mean * (i + 1)))
+             for i, p in enumerate(model.parameters()))
+    again = [None if p.grad is None else p.grad.clone() for p in model.parameters()]
+    reducer.step()  # averaging an already equal gradient leaves it unchanged
+    stable = all(a is None or torch.allclose(a, p.grad) for a, p in zip(again, model.parameters()))
+    reducer.free()
+    return ok, stable, model[0].bias.grad is None
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_data_parallel_gradient_averaging(world):
+    for value in run_ranks(_gradient_averaging, world).values():
+        assert value == (True, True, True)
+
+
+def _tensor_parallel_layers(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+    from mnnvl_sharp_b200.models import RowParallelLinearFP8, TensorParallelFFN
+
+    world = comm.world
+    layer = RowParallelLinearFP8(comm, in_features=128 * world, out_features=128, max_tokens=128, seed=3)
+    torch.manual_seed(5)
+    x_full = torch.randn(128, 128 * world)
+    x_local = x_full[:, comm.rank * layer.k_local:(comm.rank + 1) * layer.k_local].contiguous()
+    boot.barrier()
+    y = layer(x_local).float().clone()
+    total = boot.allgather_array(layer.reference(x_local).numpy()).sum(axis=0)
+    linear_err = float(np.abs(y.numpy() - total).max() / np.abs(total).max())
+    same = len(set(int(h) for h in boot.allgather_array(
+        np.array([ops.replica_hash(layer._op(128).out_buf, 128 * 128 * 2)], dtype=np.uint64))[:, 0])) == 1
+    # the full-precision product of the unsharded operands: quantisation error only
+    g = torch.Generator().manual_seed(3)
+    weight = torch.randn(128, 128 * world, generator=g) / (128 * world) ** 0.5
+    exact = x_full @ weight.t()
+    quant_err = float((y - exact).abs().max() / exact.abs().max())
+    layer.free()
+
+    ffn = TensorParallelFFN(comm, hidden=128, intermediate=128 * world, max_tokens=128, seed=7)
+    tokens = torch.randn(128, 128, generator=torch.Generator().manual_seed(11))
+    boot.barrier()
+    z = ffn(tokens).float().clone()
+    want = boot.allgather_array(ffn.reference(tokens).numpy()).sum(axis=0)
+    ffn_err = float(np.abs(z.numpy() - want).max() / np.abs(want).max())
+    ffn.free()
+    return linear_err, same, quant_err, ffn_err, tuple(y.shape), str(y.dtype)
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_tensor_parallel_layers_match_the_sum_of_partial_products(world):
+    for linear_err, same, quant_err, ffn_err, shape, dtype in run_ranks(_tensor_parallel_layers, world, timeout=300).values():
+        assert linear_err < 2 ** -7 and ffn_err < 2 ** -7  # BF16 rounding of the result only
+        assert same and quant_err < 0.08 and shape == (128, 128) and dtype == "torch.float32"
