@@ -20,7 +20,13 @@ void check(int rc, const char* what) {
   }
 }
 
-uint64_t current_stream() { return reinterpret_cast<uint64_t>(at::cuda::getCurrentCUDAStream().stream()); }
+// A machine without a CUDA device can only hold communicators on the host-memory driver stand-in,
+// whose collectives the native library plays through on the CPU: no stream, CPU tensors.
+bool have_device() { return at::hasCUDA() && at::cuda::device_count() > 0; }
+
+uint64_t current_stream() {
+  return have_device() ? reinterpret_cast<uint64_t>(at::cuda::getCurrentCUDAStream().stream()) : 0;
+}
 
 void* handle(int64_t h) { return reinterpret_cast<void*>(static_cast<intptr_t>(h)); }
 
@@ -44,7 +50,7 @@ void all_reduce_sw_f32(int64_t comm, int64_t symm, int64_t offset, int64_t nbyte
                        double out_scale, int64_t grid, int64_t block) {
   uint64_t scales = 0;
   if (in_scales.has_value()) {
-    TORCH_CHECK(in_scales->is_cuda() && in_scales->scalar_type() == at::kFloat && in_scales->is_contiguous(),
+    TORCH_CHECK(in_scales->is_cuda() == have_device() && in_scales->scalar_type() == at::kFloat && in_scales->is_contiguous(),
                 "in_scales must be a contiguous float32 CUDA tensor");
     scales = reinterpret_cast<uint64_t>(in_scales->data_ptr());
   }
@@ -63,7 +69,10 @@ void all_reduce_bulk_push(int64_t comm, int64_t symm, std::string dtype, int64_t
 // Fused block-scaled FP8 GEMM + all-reduce into the symmetric BF16 buffer `out_symm`.
 void gemm_allreduce(int64_t comm, int64_t out_symm, const at::Tensor& a, const at::Tensor& a_scales, const at::Tensor& w,
                     const at::Tensor& w_scales, int64_t reducer_ctas) {
-  TORCH_CHECK(a.is_cuda() && w.is_cuda() && a_scales.is_cuda() && w_scales.is_cuda(), "operands must be CUDA tensors");
+  const bool on_device = have_device();
+  TORCH_CHECK(a.is_cuda() == on_device && w.is_cuda() == on_device && a_scales.is_cuda() == on_device &&
+                  w_scales.is_cuda() == on_device,
+              "operands must be CUDA tensors");
   TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && a.size(1) == w.size(1), "A is [M, K], W is [N, K]");
   TORCH_CHECK(a.is_contiguous() && w.is_contiguous() && a_scales.is_contiguous() && w_scales.is_contiguous(),
               "operands must be contiguous");
@@ -81,7 +90,8 @@ void gemm_allreduce(int64_t comm, int64_t out_symm, const at::Tensor& a, const a
 // A tensor that views `nbytes` of device memory at `ptr` (symmetric memory is not owned by
 // PyTorch's allocator). The caller keeps the allocation alive.
 at::Tensor tensor_from_ptr(int64_t ptr, int64_t nbytes, int64_t device) {
-  auto options = at::TensorOptions().dtype(at::kByte).device(at::kCUDA, static_cast<c10::DeviceIndex>(device));
+  auto options = have_device() ? at::TensorOptions().dtype(at::kByte).device(at::kCUDA, static_cast<c10::DeviceIndex>(device))
+                               : at::TensorOptions().dtype(at::kByte).device(at::kCPU);
   return at::from_blob(reinterpret_cast<void*>(static_cast<intptr_t>(ptr)), {nbytes}, [](void*) {}, options);
 }
 

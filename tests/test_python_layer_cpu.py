@@ -157,6 +157,56 @@ def test_operator_argument_errors_are_raised_on_every_rank_before_any_collective
         assert seen == ["ValueError", "ValueError", "ValueError", "NativeError", "ValueError", "NativeError"]
 
 
+def _torch_library_ops(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200.ops import quantize_blockwise, reference_fp32, torch_ops
+
+    world = comm.world
+    buf = comm.alloc(8192, layout="input_output", multicast=False)
+    view = torch_ops.tensor_from_ptr(buf.output_ptr(), 8192, 0).view(torch.float16)
+    view.fill_(float(comm.rank + 1))
+    boot.barrier()
+    torch.ops.msharp.all_reduce_pull(comm.handle, buf.handle, "f16", True, 0, 8192, 0, 0, 0)
+    pull_ok = bool((view == world * (world + 1) / 2).all())
+    src = torch_ops.tensor_from_ptr(buf.input_ptr(), 8192, 0).view(torch.float16)
+    src.fill_(0.25)
+    boot.barrier()
+    torch_ops.all_reduce_bulk_push(comm, buf, "f16")
+    push_ok = bool((view == 0.25 * world).all())
+    codes = torch_ops.tensor_from_ptr(buf.output_ptr(), 4096, 0)
+    codes.fill_(0x38)  # 1.0 in E4M3
+    boot.barrier()
+    torch_ops.all_reduce_sw_f32(comm, buf, nbytes=4096, in_scales=torch.full((world,), 0.5), out_scale=1.0)
+    sw_ok = bool((codes == {1: 0x30, 2: 0x38, 4: 0x40}[world]).all())  # 0.5 * world
+    del view, src, codes
+    buf.free()
+
+    torch.manual_seed(1 + comm.rank)
+    a, sa = quantize_blockwise(torch.randn(128, 256) / 16, 1)
+    w, sw = quantize_blockwise(torch.randn(128, 256) / 16, 128)
+    out = comm.alloc(128 * 128 * 2)
+    torch_ops.gemm_allreduce(comm, out, a, sa, w, sw)
+    got = torch_ops.tensor_from_ptr(out.output_ptr(), 128 * 128 * 2, 0).view(torch.bfloat16).view(128, 128).float().clone()
+    want = boot.allgather_array(reference_fp32(a, sa, w, sw).numpy()).sum(axis=0)
+    gemm_err = float(np.abs(got.numpy() - want).max() / np.abs(want).max())
+    refused = ""
+    try:
+        torch_ops.gemm_allreduce(comm, out, a, sa, w[:, :128].contiguous(), sw)
+    except Exception as ex:  # noqa: BLE001
+        refused = str(ex)
+    boot.barrier()
+    out.free()
+    return pull_ok, push_ok, sw_ok, gemm_err, "A is [M, K], W is [N, K]" in refused
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_torch_library_operators(world):
+    for pull_ok, push_ok, sw_ok, gemm_err, refused in run_ranks(_torch_library_ops, world).values():
+        assert pull_ok and push_ok and sw_ok and refused
+        assert gemm_err < 2 ** -7
+
+
 # ------------------------------------------------------------------------------------ layers
 def _gradient_averaging(comm, boot):
     import torch
