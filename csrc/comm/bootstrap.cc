@@ -285,26 +285,19 @@ class HubBootstrap final : public Bootstrap {
       throw BootstrapError("bootstrap: rank " + std::to_string(opt.rank) + " is outside world size " +
                            std::to_string(opt.world));
     }
-    if (opt.rank == 0) {
-      listen_and_accept();
-    } else {
-      connect_to_hub();
+    try {
+      if (opt.rank == 0) {
+        listen_and_accept();
+      } else {
+        connect_to_hub();
+      }
+    } catch (...) {
+      close_all();  // a constructor that throws gets no destructor call
+      throw;
     }
   }
 
-  ~HubBootstrap() override {
-    for (int fd : peers_) {
-      if (fd >= 0) {
-        ::close(fd);
-      }
-    }
-    if (hub_ >= 0) {
-      ::close(hub_);
-    }
-    if (listener_ >= 0) {
-      ::close(listener_);
-    }
-  }
+  ~HubBootstrap() override { close_all(); }
 
   int rank() const override { return opt_.rank; }
   int world() const override { return opt_.world; }
@@ -395,6 +388,23 @@ class HubBootstrap final : public Bootstrap {
   }
 
  private:
+  void close_all() noexcept {
+    for (int& fd : peers_) {
+      if (fd >= 0) {
+        ::close(fd);
+        fd = -1;
+      }
+    }
+    if (hub_ >= 0) {
+      ::close(hub_);
+      hub_ = -1;
+    }
+    if (listener_ >= 0) {
+      ::close(listener_);
+      listener_ = -1;
+    }
+  }
+
   void check_root(int root) const {
     if (root < 0 || root >= opt_.world) {
       throw BootstrapError("bootstrap: root " + std::to_string(root) + " is outside the world");
