@@ -121,3 +121,51 @@ def device_hash(ptr: int, nbytes: int) -> int:
     out = torch.zeros(1, dtype=torch.int64, device="cuda")
     N.check(N.lib.msharp_hash_device(ptr, nbytes, out.data_ptr(), _stream()))
     return int(out.item()) & 0xFFFFFFFFFFFFFFFF
+
+
+class StagedAllReduce:
+    """All-reduce (sum or mean) of ordinary tensors, i.e. tensors that do not live in symmetric memory.
+
+    The in-switch kernels work on symmetric buffers. For a tensor from PyTorch's own allocator this
+    helper owns one symmetric staging buffer, copies the tensor in (in pieces when it is larger than
+    the buffer), reduces each piece in place with the pull kernel (float32 accumulation in the
+    switch) and copies the result back, all on the current stream. FP16 and BF16 tensors only: those
+    are the 16-bit types the switch reduces. Collective: every rank calls it with the same shape."""
+
+    _CODES = {torch.float16: "f16", torch.bfloat16: "bf16"}
+
+    def __init__(self, comm: Communicator, max_bytes: int = 64 << 20):
+        if max_bytes < 16 or max_bytes % 16:
+            raise ValueError("max_bytes must be a positive multiple of 16")
+        self.comm = comm
+        self.max_bytes = max_bytes
+        self.buf = comm.alloc(max_bytes, layout="single", multicast=True)
+        self._views = {dt: self.buf.tensor(dt) for dt in self._CODES}
+
+    @torch.no_grad()
+    def __call__(self, tensor: torch.Tensor, average: bool = False) -> torch.Tensor:
+        code = self._CODES.get(tensor.dtype)
+        if code is None:
+            raise ValueError("StagedAllReduce handles float16 and bfloat16 tensors")
+        if not tensor.is_contiguous():
+            raise ValueError("the tensor must be contiguous (it is reduced in place)")
+        flat = tensor.view(-1)
+        stage = self._views[tensor.dtype]
+        per_piece = self.max_bytes // 2
+        for start in range(0, flat.numel(), per_piece):
+            piece = flat[start:start + per_piece]
+            n = piece.numel()
+            stage[:n].copy_(piece)
+            nbytes = ((n * 2 + 3) // 4) * 4  # the kernels move whole 32-bit words
+            if nbytes != n * 2:
+                stage[n:n + 1].zero_()
+            all_reduce_pull(self.comm, self.buf, code, nbytes=nbytes)
+            piece.copy_(stage[:n])
+        if average:
+            flat.mul_(1.0 / self.comm.world)
+        return tensor
+
+    def free(self) -> None:
+        """Collective."""
+        self._views = {}
+        self.buf.free()

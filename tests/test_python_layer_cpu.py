@@ -157,6 +157,41 @@ def test_operator_argument_errors_are_raised_on_every_rank_before_any_collective
         assert seen == ["ValueError", "ValueError", "ValueError", "NativeError", "ValueError", "NativeError"]
 
 
+def _staged(comm, boot):
+    import torch
+
+    from mnnvl_sharp_b200 import ops
+
+    world = comm.world
+    staged = ops.StagedAllReduce(comm, max_bytes=4096)  # small on purpose: larger tensors go through in pieces
+    results = []
+    for dtype, shape in [(torch.float16, (7,)), (torch.bfloat16, (33, 65)), (torch.float16, (4096,))]:
+        t = torch.full(shape, float(comm.rank + 1), dtype=dtype)
+        t.view(-1)[0] = 0.5 * (comm.rank + 1)
+        boot.barrier()
+        back = staged(t)
+        total = world * (world + 1) / 2
+        results.append(back is t and float(t.view(-1)[0]) == 0.5 * total and bool((t.view(-1)[1:] == total).all()))
+    mean = staged(torch.full((10,), float(comm.rank), dtype=torch.bfloat16), average=True)
+    results.append(bool((mean == (world - 1) / 2).all()))
+    refused = []
+    for bad in (torch.ones(4), torch.ones(4, 4, dtype=torch.float16).t()):
+        try:
+            staged(bad)
+            refused.append(False)
+        except ValueError:
+            refused.append(True)
+    boot.barrier()
+    staged.free()
+    return results, refused
+
+
+@pytest.mark.parametrize("world", [1, 3])
+def test_staged_all_reduce_of_ordinary_tensors(world):
+    for results, refused in run_ranks(_staged, world).values():
+        assert results == [True, True, True, True] and refused == [True, True]
+
+
 def _torch_library_ops(comm, boot):
     import torch
 
