@@ -40,7 +40,11 @@ def main() -> int:
     p.add_argument("--csv", default="")
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--graph", action="store_true", help="time CUDA-graph replays (no host launch cost)")
+    p.add_argument("--phases", action="store_true",
+                   help="after timing a point, run it once more with in-kernel phase stamps and add, per phase, the "
+                        "maximum over ranks in microseconds (opening barrier, data movement, closing barrier)")
     args = p.parse_args()
+    fields = FIELDS + (["entry_barrier_us", "transfer_us", "exit_barrier_us"] if args.phases else [])
 
     boot, comm = init_rank()
     world, rank = comm.world, comm.rank
@@ -54,7 +58,7 @@ def main() -> int:
     if rank == 0 and args.csv:
         new = not os.path.exists(args.csv)
         f = open(args.csv, "a", newline="")
-        writer = csv.DictWriter(f, fieldnames=FIELDS)
+        writer = csv.DictWriter(f, fieldnames=fields)
         if new:
             writer.writeheader()
 
@@ -86,9 +90,20 @@ def main() -> int:
             iters = args.iters if nbytes >= (1 << 20) else args.iters * 5
             ms = time_steps(boot, comm, lambda: ops.all_reduce(comm, buf, dtype, backend=backend, nbytes=nbytes), iters,
                             graph=args.graph)
-            emit({"world": world, "impl": "ours", "backend": backend, "dtype": dtype, "bytes": nbytes, "ms": round(ms, 6),
-                  "algbw_gb_s": round(nbytes / (ms * 1e6), 3), "busbw_gb_s": round(busbw(nbytes, ms, world), 3),
-                  "timing": "graph" if args.graph else "launch"})
+            row = {"world": world, "impl": "ours", "backend": backend, "dtype": dtype, "bytes": nbytes, "ms": round(ms, 6),
+                   "algbw_gb_s": round(nbytes / (ms * 1e6), 3), "busbw_gb_s": round(busbw(nbytes, ms, world), 3),
+                   "timing": "graph" if args.graph else "launch"}
+            if args.phases:
+                comm.set_trace(True)
+                torch.cuda.synchronize()
+                boot.barrier()
+                ops.all_reduce(comm, buf, dtype, backend=backend, nbytes=nbytes)
+                torch.cuda.synchronize()
+                comm.set_trace(False)
+                mine = comm.phase_times_us()
+                for key in ("entry_barrier_us", "transfer_us", "exit_barrier_us"):
+                    row[key] = round(boot.reduce_max(mine[key]), 3)
+            emit(row)
 
     if args.nccl and world > 1:
         import torch.distributed as dist
