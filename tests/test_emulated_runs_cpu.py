@@ -67,6 +67,24 @@ def test_a_wrong_value_in_the_checked_prefix_is_counted_and_fails_the_run():
     assert "got" in done.stderr and "expected" in done.stderr  # the mismatch dump asked for by MNNVL_DEBUG_MISMATCH
 
 
+def test_zero_iterations_still_produce_a_checked_result_and_init_only_stops_after_the_canary():
+    # --iters 0: one unmeasured iteration runs so that the check has data (reference: src/main.cc:446-448)
+    done = run_binary("--json", "--bytes", "65536", "--reference-check-bytes", "4096", "--iters", "0", "--warmup", "0", ranks=2)
+    assert done.returncode == 0
+    r = last_json(done.stdout)
+    assert r["hashes_match"] is True and r["semantic_exact_mismatches"] == 0
+    assert r["sharp_kernel_ms"] == {"min": 0, "median": 0, "p95": 0, "max": 0}
+    # the default --reference-check-bytes (16 MiB) exceeds small --bytes: refused as in the reference (config.cc:159-161)
+    done = run_binary("--bytes", "65536", "--init-only", ranks=2)
+    assert done.returncode == 1 and "--reference-check-bytes cannot exceed --bytes" in done.stderr
+    done = run_binary("--bytes", "65536", "--reference-check-bytes", "4096", "--init-only", ranks=2)
+    assert done.returncode == 0
+    assert "smoke_test: passed" in done.stdout and "sharp_allreduce: skipped" in done.stdout
+    done = run_binary("--bytes", "65536", "--reference-check-bytes", "4096", "--init-only", "--json", ranks=2)
+    r = last_json(done.stdout)
+    assert r["init_only"] is True and r["hashes_match"] is None and r["hashes"] == [] and r["f32_max_abs_error"] is None
+
+
 def test_human_report_of_a_full_run():
     done = run_binary("--bytes", "1048576", "--reference-check-bytes", "4096")
     assert done.returncode == 0
