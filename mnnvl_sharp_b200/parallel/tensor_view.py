@@ -29,6 +29,5 @@ def host_tensor(ptr: int, nbytes: int, dtype: torch.dtype, owner=None) -> torch.
     import ctypes
 
     array = (ctypes.c_uint8 * nbytes).from_address(ptr)
-    raw = torch.frombuffer(array, dtype=torch.uint8)
-    raw._msharp_owner = owner  # keeps the allocation alive as long as this tensor object
-    return raw.view(dtype)
+    array._owner = owner  # torch keeps `array` alive as long as any view of the storage; it keeps the allocation
+    return torch.frombuffer(array, dtype=torch.uint8).view(dtype)
