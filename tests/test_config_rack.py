@@ -263,3 +263,50 @@ def test_cpu_only_binary_dumps_the_bitwise_expected_result(tmp_path):
 def test_csv_header():
     assert rack.CSV_HEADER == ("rank_count,repeat,sharp_backend,peer_init_ms,peer_init_min_ms,peer_init_median_ms,"
                                "peer_init_p95_ms,peer_init_max_ms")
+
+
+def _inventory_yaml(trays):
+    lines = ["rack:"]
+    for i, devices in enumerate(trays):
+        lines += [f"  - tray{i:02d}:", f"      - hostname: 10.0.0.{i + 1}", f"      - device: {list(devices)}"]
+    return "\n".join(lines) + "\n"
+
+
+def test_rank_plan_invariants_over_random_inventories():
+    """For any inventory and count: every selected (tray, device) pair is distinct and listed in the
+    inventory; `prefix` fills trays in inventory order; `balanced` takes device slot s of every tray
+    before slot s + 1 (so per-tray counts differ by at most one while trays still have devices)."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    trays_strategy = st.lists(
+        st.lists(st.integers(min_value=0, max_value=15), min_size=1, max_size=8, unique=True), min_size=1, max_size=9)
+
+    @settings(max_examples=150, deadline=None)
+    @given(trays=trays_strategy, data=st.data())
+    def check(trays, data):
+        text = _inventory_yaml(trays)
+        total = sum(len(t) for t in trays)
+        count = data.draw(st.integers(min_value=1, max_value=total))
+        for policy in ("prefix", "balanced"):
+            plan = rack.rank_plan(text, count, policy)
+            assert [t["rank"] for t in plan] == list(range(count))
+            pairs = [(t["rack_index"], t["gpu"]) for t in plan]
+            assert len(set(pairs)) == count
+            assert all(gpu in trays[tray] for tray, gpu in pairs)
+            per_tray = [sum(1 for tray, _ in pairs if tray == i) for i in range(len(trays))]
+            for t in plan:  # local rank = position among the ranks of the same tray
+                assert t["local_rank"] == [p for p in plan if p["rack_index"] == t["rack_index"]].index(t)
+            if policy == "prefix":
+                flat = [(i, g) for i, devices in enumerate(trays) for g in devices]
+                assert pairs == flat[:count]
+            else:
+                slots = [(i, devices[s]) for s in range(8) for i, devices in enumerate(trays) if s < len(devices)]
+                assert pairs == slots[:count]
+                unfilled = [n for n, devices in zip(per_tray, trays) if n < len(devices)]
+                if unfilled:
+                    assert max(per_tray) - min(unfilled) <= 1
+        with pytest.raises(NativeError):
+            rack.rank_plan(text, total + 1, "balanced")
+
+    check()
