@@ -240,6 +240,56 @@ void test_codec_spot_checks() {
   EXPECT(reference_f16_bits(0, 0) == 0x0000);  // mix = 7 -> table entry 7
 }
 
+// The control plane at the size of a full rack: 72 ranks (threads here) over Unix-domain sockets.
+void test_control_plane_at_rack_scale() {
+  using namespace msharp;
+  const int world = kMaxRanks;
+  std::vector<std::string> errors(world);
+  std::vector<std::thread> threads;
+  const std::string session = "cpp-rack-" + std::to_string(getpid());
+  for (int rank = 0; rank < world; ++rank) {
+    threads.emplace_back([&, rank] {
+      try {
+        BootstrapOptions opt;
+        opt.rank = rank;
+        opt.world = world;
+        opt.session = session;
+        opt.timeout_ms = 30000;
+        std::unique_ptr<Bootstrap> comm = Bootstrap::connect(opt);
+        for (int round = 0; round < 3; ++round) {
+          const std::vector<uint64_t> all = comm->allgather_u64(static_cast<uint64_t>(rank * 1000 + round));
+          for (int r = 0; r < world; ++r) {
+            if (all[static_cast<std::size_t>(r)] != static_cast<uint64_t>(r * 1000 + round)) {
+              throw std::runtime_error("allgather returned the wrong value");
+            }
+          }
+          if (comm->broadcast_int(rank == world - 1 ? 4242 + round : -1, world - 1) != 4242 + round) {
+            throw std::runtime_error("broadcast returned the wrong value");
+          }
+          if (comm->all_true(rank != 17) || !comm->all_true(true)) {
+            throw std::runtime_error("all_true is wrong");
+          }
+          comm->barrier();
+        }
+        if (comm->reduce_max(static_cast<double>(rank)) != world - 1 || comm->reduce_min(static_cast<double>(rank)) != 0) {
+          throw std::runtime_error("reduce_max / reduce_min is wrong");
+        }
+      } catch (const std::exception& ex) {
+        errors[static_cast<std::size_t>(rank)] = ex.what();
+      }
+    });
+  }
+  for (std::thread& t : threads) {
+    t.join();
+  }
+  for (int rank = 0; rank < world; ++rank) {
+    if (!errors[static_cast<std::size_t>(rank)].empty()) {
+      std::printf("rank %d: %s\n", rank, errors[static_cast<std::size_t>(rank)].c_str());
+    }
+    EXPECT(errors[static_cast<std::size_t>(rank)].empty());
+  }
+}
+
 // Mutated inventories and CLI words through the parsers: every input must end in a value or an
 // exception, never in a crash, a hang or a sanitizer report.
 void test_parsers_survive_mutated_input() {
@@ -420,6 +470,7 @@ int main() {
   test_codec_spot_checks();
   test_tcp_control_plane_and_fabric_handles();
   test_parsers_survive_mutated_input();
+  test_control_plane_at_rack_scale();
   if (g_failures == 0) {
     std::printf("all native tests passed\n");
     return 0;
