@@ -173,6 +173,50 @@ def test_multi_host_launch_end_to_end_without_gpus(tmp_path, monkeypatch, capfd)
     assert len(report["peer_init_local_ms_by_rank"]) == 4
 
 
+def test_full_nvl72_rack_launch_without_gpus(tmp_path, monkeypatch, capfd):
+    """The reference's target configuration, 18 trays of 4 GPUs and 72 ranks with the balanced plan,
+    through the launcher: 18 per-tray copies of the binary, 72 rank processes, TCP control plane,
+    fabric handles, 72-slot symmetric buffers, canary of all 72 slots on every rank, iterations."""
+    import json
+    import re
+    import socket
+    import stat
+
+    from mnnvl_sharp_b200 import _build
+
+    _build.build_native()
+    source = (Path(__file__).resolve().parents[1] / "examples" / "rack_nvl72.yaml").read_text()
+    rack_path = tmp_path / "rack.yaml"
+    rack_path.write_text(re.sub(r"hostname: [0-9.]+", "hostname: 127.0.0.1", source))
+    fake_ssh = tmp_path / "fake_ssh"
+    fake_ssh.write_text("#!/bin/sh\nshift 3\nexec sh -c \"$1\"\n")
+    fake_scp = tmp_path / "fake_scp"
+    fake_scp.write_text("#!/bin/sh\nexec cp \"$3\" \"${4#*:}\"\n")
+    for f in (fake_ssh, fake_scp):
+        f.chmod(f.stat().st_mode | stat.S_IEXEC)
+    app_dir = tmp_path / "app"
+    (app_dir / "mnnvl_sharp_b200" / "_C").mkdir(parents=True)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    for key, value in {"MNNVL_SSH_COMMAND": fake_ssh, "MNNVL_SCP_COMMAND": fake_scp, "MNNVL_SKIP_REMOTE_BUILD": "1",
+                       "MNNVL_APP_DIR": app_dir, "MNNVL_LOCAL_LABEL": "nvl72-tray00", "MSHARP_HUB_PORT": port,
+                       "MSHARP_DRIVER": "fake", "MSHARP_FAKE_FABRIC": "1", "MSHARP_BOOTSTRAP_TIMEOUT_MS": "60000"}.items():
+        monkeypatch.setenv(key, str(value))
+    rc = run.main([str(rack_path), "--rank-count", "72", "--json", "--no-pin", "--bytes", "1048576",
+                   "--reference-check-bytes", "65536", "--warmup", "1", "--iters", "1", "--pattern", "seeded"])
+    out = capfd.readouterr().out
+    assert rc == 0, out[-3000:]
+    report = json.loads([line for line in out.splitlines() if line.startswith("{")][-1])
+    assert report["selected_rank_count"] == 72 and report["handle_type"] == "fabric" and report["status"] == 0
+    assert report["hashes_match"] is True and len(report["hashes"]) == 72 and len(report["peer_init_local_ms_by_rank"]) == 72
+    mapping = report["host_mapping"]
+    # balanced: ranks 0..17 are device 0 of trays 0..17, ranks 18..35 device 1, ...
+    assert [(m["rack_index"], m["gpu"], m["local_rank"]) for m in mapping[:3]] == [(0, 0, 0), (1, 0, 0), (2, 0, 0)]
+    assert (mapping[18]["rack_index"], mapping[18]["gpu"], mapping[18]["local_rank"]) == (0, 1, 1)
+    assert (mapping[71]["host_label"], mapping[71]["gpu"], mapping[71]["local_rank"]) == ("nvl72-tray17", 3, 3)
+
+
 def test_multi_host_launch_reports_a_host_that_has_no_ranks(tmp_path, monkeypatch):
     import subprocess
 
