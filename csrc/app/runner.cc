@@ -259,6 +259,168 @@ int tolerance_for(const Config& cfg, int world) {
   return resolve_acc(cfg) == AccChoice::kF32 ? 1 : world;
 }
 
+SymmOptions base_options(const RankRun& run) {
+  SymmOptions base;
+  base.handle_type = run.cfg.handle_type;
+  base.device_ordinal = run.rank.gpu_ordinal;
+  base.cu_device = run.rank.cu_device;
+  base.posix_fd_supported = run.caps.posix_fd_handle_supported;
+  base.fabric_supported = run.caps.fabric_handle_supported;
+  base.fabric_unusable_reason = run.caps.fabric_probe_error;
+  base.multicast_supported = run.caps.multicast_supported;
+  return base;
+}
+
+const char* kernel_variant_name(const RankRun& run) {
+  const Config& cfg = run.cfg;
+  const int world = run.rank.world_size;
+  if (run.api.is_fake) {
+    return "host_emulation_f32_sum";
+  }
+  switch (cfg.sharp_backend) {
+    case Backend::kLegacy:
+    case Backend::kPull:
+      return world == 1 ? "local_copy" : cfg.reference_geometry ? "reference_geometry_rank0_b32" : "multimem_ld_reduce_st_v4_sliced";
+    case Backend::kSwF32:
+      return run.mem->mc_base != 0 ? "peer_loads_f32_multimem_st" : "peer_loads_f32_peer_stores";
+    case Backend::kTmaAsync:
+      return "bulk_ring_store_reduce";
+  }
+  return "";
+}
+
+// Control block and data buffer (both collective), with the timed peer-init phase inside the latter.
+void allocate_buffers(RankRun& run, RunReport& report) {
+  const Config& cfg = run.cfg;
+  const SymmOptions base = base_options(run);
+  const auto c0 = Clock::now();
+  nvtxRangePushA("control_block_init");
+  run.ctx = CommContext::create(run.api, run.comm, base, cfg.wait_timeout_ms);
+  nvtxRangePop();
+  report.control_init_ms = ms_since(c0);
+
+  SymmOptions data = base;
+  data.payload_bytes = cfg.bytes;
+  data.layout = cfg.sharp_backend == Backend::kTmaAsync ? RegionLayout::kInputOutput : RegionLayout::kSingle;
+  // the fan-out form of the bulk backend and the software path write through unicast mappings
+  data.want_multicast = cfg.sharp_backend != Backend::kTmaAsync || bulk_multimem_compiled();
+  nvtxRangePushA("symmetric_memory_init");
+  run.mem = SymmetricMemory::create(run.api, run.comm, data);
+  nvtxRangePop();
+  if ((cfg.sharp_backend == Backend::kLegacy || cfg.sharp_backend == Backend::kPull) && run.rank.world_size > 1 &&
+      run.mem->mc_base == 0) {
+    throw std::runtime_error("the multicast alias could not be created; this backend needs it");
+  }
+
+  report.allocation_bytes = run.mem->alloc_bytes;
+  report.input_offset = run.mem->input_offset;
+  report.output_offset = run.mem->output_offset;
+  report.multicast_bytes = run.mem->multicast_bytes;
+  report.vmm_granularity = run.mem->vmm_granularity;
+  report.multicast_granularity = run.mem->multicast_granularity;
+  report.peer_init = summarize(run.mem->peer_init_all_ms);
+  report.peer_init_by_rank = run.mem->peer_init_all_ms;
+  report.handle_kind = run.mem->handle_kind;
+  report.kernel_variant = kernel_variant_name(run);
+  if (cfg.sharp_backend == Backend::kTmaAsync && !run.api.is_fake) {
+    report.bulk_variant = "unicast_fanout";
+  }
+}
+
+uint64_t replica_hash(RankRun& run) {
+  const Config& cfg = run.cfg;
+  if (run.api.is_fake) {
+    return hash_words(static_cast<const uint32_t*>(run.output_ptr()), cfg.bytes / 4);
+  }
+  uint64_t local_hash = 0;
+  uint64_t* device_hash = run.ctx->scratch_u64();
+  launch_hash(run.output_ptr(), cfg.bytes, device_hash, run.stream);
+  MSHARP_CUDA(cudaMemcpyAsync(&local_hash, device_hash, sizeof(local_hash), cudaMemcpyDeviceToHost, run.stream));
+  MSHARP_CUDA(cudaStreamSynchronize(run.stream));
+  return local_hash;
+}
+
+// Warm-up and measured iterations, phase stamps of the last one when asked for, replica hashes.
+void measure(RankRun& run, RunReport& report) {
+  const Config& cfg = run.cfg;
+  for (int i = 0; i < cfg.warmup; ++i) {
+    run_iteration(run, false, nullptr, nullptr);
+  }
+  std::vector<double> device_times;
+  std::vector<double> wall_times;
+  for (int i = 0; i < cfg.iters; ++i) {
+    double d = 0.0;
+    double w = 0.0;
+    run_iteration(run, true, &d, &w);
+    device_times.push_back(d);
+    wall_times.push_back(w);
+  }
+  if (cfg.iters == 0) {
+    run_iteration(run, false, nullptr, nullptr);  // the check needs one result
+  }
+  if (run.ctx->trace_enabled()) {
+    const CommContext::PhaseTimes p = run.ctx->read_trace();  // stamps of the last kernel; the stream is idle
+    report.phase_entry_barrier_us = run.comm.allgather_double(p.entry_barrier_us);
+    report.phase_transfer_us = run.comm.allgather_double(p.transfer_us);
+    report.phase_exit_barrier_us = run.comm.allgather_double(p.exit_barrier_us);
+  }
+  report.hashes = run.comm.allgather_u64(replica_hash(run));
+  report.has_results = true;
+  report.device_ms = summarize(device_times);
+  report.wall_ms = summarize(wall_times);
+}
+
+// Rank 0: the first --reference-check-bytes of its replica against the host oracle.
+void check_result(RankRun& run, RunReport& report) {
+  const Config& cfg = run.cfg;
+  const int world = run.rank.world_size;
+  std::vector<unsigned char> checked(cfg.reference_check_bytes);
+  run.mem->copy_to_host(checked.data(), 0, run.mem->output_offset, checked.size());
+  InputSpec spec;
+  spec.pattern = run.pattern;
+  spec.seed = cfg.seed;
+  spec.ranks = world;
+  const std::size_t elements = cfg.reference_check_bytes / dtype_size(run.dtype);
+  report.metrics = compare(run.dtype, spec, checked.data(), elements);
+  report.tolerance_ulp = tolerance_for(cfg, world);
+  report.within_tolerance = report.metrics.max_requantized_ulp_distance <= report.tolerance_ulp;
+  if (cfg.sharp_backend == Backend::kTmaAsync && cfg.pattern == "seeded" && world > 1) {
+    // each of the world - 1 memory-side adds rounds to the element type; |partial sums| <= 6 * world
+    const double eps = run.dtype == Dtype::kBF16 ? 0x1p-8 : 0x1p-11;
+    report.tolerance_abs = static_cast<double>(world - 1) * eps * 6.0 * world;
+    report.within_tolerance = report.metrics.max_abs_error <= report.tolerance_abs;
+  }
+  if (report.metrics.exact_mismatches != 0 && std::getenv("MNNVL_DEBUG_MISMATCH") != nullptr) {
+    std::cerr << mismatch_dump(run.dtype, spec, checked.data(), elements) << "\n";
+  }
+}
+
+// Teardown in order on every path: no rank unmaps while a peer's kernel may still run.
+void teardown(RankRun& run, std::string* failure) {
+  const bool fake = run.api.is_fake;
+  if (!fake) {
+    cudaStreamSynchronize(run.stream);
+  }
+  if (failure->empty()) {
+    try {
+      run.comm.barrier();
+    } catch (const std::exception& ex) {
+      *failure = ex.what();
+    }
+  }
+  if (run.mem) {
+    run.mem->destroy();
+  }
+  if (run.ctx) {
+    run.ctx->destroy(nullptr);
+  }
+  if (!fake) {
+    cudaEventDestroy(run.stop);
+    cudaEventDestroy(run.start);
+    cudaStreamDestroy(run.stream);
+  }
+}
+
 }  // namespace
 
 int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostream& out) {
@@ -295,15 +457,6 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
     MSHARP_CUDA(cudaEventCreate(&run.stop));
   }
 
-  SymmOptions base;
-  base.handle_type = cfg.handle_type;
-  base.device_ordinal = run.rank.gpu_ordinal;
-  base.cu_device = run.rank.cu_device;
-  base.posix_fd_supported = run.caps.posix_fd_handle_supported;
-  base.fabric_supported = run.caps.fabric_handle_supported;
-  base.fabric_unusable_reason = run.caps.fabric_probe_error;
-  base.multicast_supported = run.caps.multicast_supported;
-
   RunReport report;
   report.cfg = cfg;
   report.caps = run.caps;
@@ -312,117 +465,15 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
   int status = 0;
   std::string failure;
   try {
-    const auto c0 = Clock::now();
-    nvtxRangePushA("control_block_init");
-    run.ctx = CommContext::create(api, comm, base, cfg.wait_timeout_ms);
-    nvtxRangePop();
-    report.control_init_ms = ms_since(c0);
-
-    SymmOptions data = base;
-    data.payload_bytes = cfg.bytes;
-    data.layout = cfg.sharp_backend == Backend::kTmaAsync ? RegionLayout::kInputOutput : RegionLayout::kSingle;
-    // the fan-out form of the bulk backend and the software path write through unicast mappings
-    data.want_multicast = cfg.sharp_backend != Backend::kTmaAsync || bulk_multimem_compiled();
-    nvtxRangePushA("symmetric_memory_init");
-    run.mem = SymmetricMemory::create(api, comm, data);
-    nvtxRangePop();
-    if ((cfg.sharp_backend == Backend::kLegacy || cfg.sharp_backend == Backend::kPull) && world > 1 &&
-        run.mem->mc_base == 0) {
-      throw std::runtime_error("the multicast alias could not be created; this backend needs it");
-    }
-
-    report.allocation_bytes = run.mem->alloc_bytes;
-    report.input_offset = run.mem->input_offset;
-    report.output_offset = run.mem->output_offset;
-    report.multicast_bytes = run.mem->multicast_bytes;
-    report.vmm_granularity = run.mem->vmm_granularity;
-    report.multicast_granularity = run.mem->multicast_granularity;
-    report.peer_init = summarize(run.mem->peer_init_all_ms);
-    report.peer_init_by_rank = run.mem->peer_init_all_ms;
-    report.handle_kind = run.mem->handle_kind;
-    switch (cfg.sharp_backend) {
-      case Backend::kLegacy:
-      case Backend::kPull:
-        report.kernel_variant = world == 1 ? "local_copy"
-                                : cfg.reference_geometry ? "reference_geometry_rank0_b32"
-                                                         : "multimem_ld_reduce_st_v4_sliced";
-        break;
-      case Backend::kSwF32:
-        report.kernel_variant = run.mem->mc_base != 0 ? "peer_loads_f32_multimem_st" : "peer_loads_f32_peer_stores";
-        break;
-      case Backend::kTmaAsync:
-        report.kernel_variant = "bulk_ring_store_reduce";
-        report.bulk_variant = "unicast_fanout";
-        break;
-    }
-
-    if (fake) {
-      report.kernel_variant = "host_emulation_f32_sum";
-    }
-
+    allocate_buffers(run, report);
     canary_smoke_test(run);
     run.ctx->set_trace(cfg.trace_phases && !fake);
-
     if (!cfg.init_only) {
-      for (int i = 0; i < cfg.warmup; ++i) {
-        run_iteration(run, false, nullptr, nullptr);
-      }
-      std::vector<double> device_times;
-      std::vector<double> wall_times;
-      for (int i = 0; i < cfg.iters; ++i) {
-        double d = 0.0;
-        double w = 0.0;
-        run_iteration(run, true, &d, &w);
-        device_times.push_back(d);
-        wall_times.push_back(w);
-      }
-      if (cfg.iters == 0) {
-        run_iteration(run, false, nullptr, nullptr);  // the check below needs one result
-      }
-      if (cfg.trace_phases && !fake) {
-        const CommContext::PhaseTimes p = run.ctx->read_trace();  // stamps of the last kernel; the stream is idle
-        report.phase_entry_barrier_us = comm.allgather_double(p.entry_barrier_us);
-        report.phase_transfer_us = comm.allgather_double(p.transfer_us);
-        report.phase_exit_barrier_us = comm.allgather_double(p.exit_barrier_us);
-      }
-
-      uint64_t local_hash = 0;
-      if (fake) {
-        local_hash = hash_words(static_cast<const uint32_t*>(run.output_ptr()), cfg.bytes / 4);
-      } else {
-        uint64_t* device_hash = run.ctx->scratch_u64();
-        launch_hash(run.output_ptr(), cfg.bytes, device_hash, run.stream);
-        MSHARP_CUDA(cudaMemcpyAsync(&local_hash, device_hash, sizeof(local_hash), cudaMemcpyDeviceToHost, run.stream));
-        MSHARP_CUDA(cudaStreamSynchronize(run.stream));
-      }
-      report.hashes = comm.allgather_u64(local_hash);
-      report.has_results = true;
-      report.device_ms = summarize(device_times);
-      report.wall_ms = summarize(wall_times);
-
+      measure(run, report);
       if (comm.rank() == 0) {
-        std::vector<unsigned char> checked(cfg.reference_check_bytes);
-        run.mem->copy_to_host(checked.data(), 0, run.mem->output_offset, checked.size());
-        InputSpec spec;
-        spec.pattern = run.pattern;
-        spec.seed = cfg.seed;
-        spec.ranks = world;
-        const std::size_t elements = cfg.reference_check_bytes / dtype_size(run.dtype);
-        report.metrics = compare(run.dtype, spec, checked.data(), elements);
-        report.tolerance_ulp = tolerance_for(cfg, world);
-        report.within_tolerance = report.metrics.max_requantized_ulp_distance <= report.tolerance_ulp;
-        if (cfg.sharp_backend == Backend::kTmaAsync && cfg.pattern == "seeded" && world > 1) {
-          // each of the world - 1 memory-side adds rounds to the element type; |partial sums| <= 6 * world
-          const double eps = run.dtype == Dtype::kBF16 ? 0x1p-8 : 0x1p-11;
-          report.tolerance_abs = static_cast<double>(world - 1) * eps * 6.0 * world;
-          report.within_tolerance = report.metrics.max_abs_error <= report.tolerance_abs;
-        }
-        if (report.metrics.exact_mismatches != 0 && std::getenv("MNNVL_DEBUG_MISMATCH") != nullptr) {
-          std::cerr << mismatch_dump(run.dtype, spec, checked.data(), elements) << "\n";
-        }
+        check_result(run, report);
       }
     }
-
     if (comm.rank() == 0) {
       // grid/block as launched are reported by the launcher's own choice when left at 0
       report.grid = cfg.grid;
@@ -439,28 +490,7 @@ int run_rank(const Config& cfg, Bootstrap& comm, const DriverApi& api, std::ostr
     failure = ex.what();
   }
 
-  // Teardown in order on every path: no rank unmaps while a peer's kernel may still run.
-  if (!fake) {
-    cudaStreamSynchronize(run.stream);
-  }
-  if (failure.empty()) {
-    try {
-      comm.barrier();
-    } catch (const std::exception& ex) {
-      failure = ex.what();
-    }
-  }
-  if (run.mem) {
-    run.mem->destroy();
-  }
-  if (run.ctx) {
-    run.ctx->destroy(nullptr);
-  }
-  if (!fake) {
-    cudaEventDestroy(run.stop);
-    cudaEventDestroy(run.start);
-    cudaStreamDestroy(run.stream);
-  }
+  teardown(run, &failure);
   if (!failure.empty()) {
     throw std::runtime_error(failure);
   }
