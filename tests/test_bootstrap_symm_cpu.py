@@ -5,7 +5,6 @@ allocations are memfd files, so exported handles really travel between processes
 canary of every rank is really read by every other rank. Failures are injected on the host:
 a rank that never joins, a rank that dies, a stranger on the socket, a driver call that fails.
 """
-import multiprocessing as mp
 import os
 import socket
 import struct
@@ -14,7 +13,8 @@ import time
 import numpy as np
 import pytest
 
-CTX = mp.get_context("spawn")
+from _procs import run_processes
+
 CUDA_ERROR_NOT_SUPPORTED = 801
 CUDA_ERROR_NOT_PERMITTED = 800
 CUDA_ERROR_OUT_OF_MEMORY = 2
@@ -22,25 +22,7 @@ CUDA_ERROR_OUT_OF_MEMORY = 2
 
 def _run(target, world, *args, timeout=60):
     """Run target(rank, world, session, queue, *args) in `world` processes; return results by rank."""
-    session = f"test{os.getpid()}_{time.monotonic_ns()}"
-    q = CTX.Queue()
-    procs = [CTX.Process(target=target, args=(r, world, session, q) + args) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = {}
-    deadline = time.time() + timeout
-    while len(results) < world and time.time() < deadline:
-        try:
-            rank, value = q.get(timeout=0.5)
-            results[rank] = value
-        except Exception:
-            if all(not p.is_alive() for p in procs) and q.empty():
-                break
-    for p in procs:
-        p.join(timeout=10)
-        if p.is_alive():
-            p.kill()
-    return results
+    return run_processes(target, world, args, timeout, prefix="test")
 
 
 def _collectives(rank, world, session, q):

@@ -5,7 +5,6 @@ cannot be passed, so symmetric memory is shared through fabric handles. The fake
 in for the GPUs and for IMEX: its fabric handle is the name of a shared-memory object that any
 process of this machine can open. All ranks run on this machine and use 127.0.0.1.
 """
-import multiprocessing as mp
 import os
 import socket
 import struct
@@ -14,7 +13,7 @@ import time
 import numpy as np
 import pytest
 
-CTX = mp.get_context("spawn")
+from _procs import CTX, run_processes  # noqa: E402
 FABRIC_SUPPORTED = 128  # CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED
 
 
@@ -25,29 +24,11 @@ def free_port() -> int:
 
 
 def run_ranks(target, world, *args, timeout=60):
-    session = f"tcp{os.getpid()}_{time.monotonic_ns()}"
-    address = f"127.0.0.1:{free_port()}"
-    q = CTX.Queue()
-    procs = [CTX.Process(target=target, args=(r, world, session, address, q) + args) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = {}
-    deadline = time.time() + timeout
-    while len(results) < world and time.time() < deadline:
-        try:
-            rank, value = q.get(timeout=0.5)
-            results[rank] = value
-        except Exception:
-            if all(not p.is_alive() for p in procs) and q.empty():
-                break
-    for p in procs:
-        p.join(timeout=10)
-        if p.is_alive():
-            p.kill()
-    return results
+    """target(rank, world, session, queue, address, *args); all ranks on this machine, one fresh port."""
+    return run_processes(target, world, (f"127.0.0.1:{free_port()}",) + args, timeout, prefix="tcp")
 
 
-def _collectives(rank, world, session, address, q):
+def _collectives(rank, world, session, q, address):
     from mnnvl_sharp_b200.parallel import Bootstrap
 
     try:
@@ -76,7 +57,7 @@ def test_collectives_over_tcp(world):
         assert r["can"] is False and "cannot be passed over TCP" in r["fd_error"]
 
 
-def _other_session(rank, world, session, address, q):
+def _other_session(rank, world, session, q, address):
     from mnnvl_sharp_b200._native import NativeError
     from mnnvl_sharp_b200.parallel import Bootstrap
 
@@ -96,7 +77,7 @@ def test_a_rank_of_another_session_is_turned_away():
     assert res[1] != "joined" and ("lost the connection" in res[1] or "timed out" in res[1]), res
 
 
-def _stranger(rank, world, session, address, q):
+def _stranger(rank, world, session, q, address):
     from mnnvl_sharp_b200.parallel import Bootstrap
 
     if rank == 1:
@@ -124,7 +105,7 @@ def test_a_bad_address_is_refused_with_a_message():
             Bootstrap(1, 2, "s", timeout_ms=200, address=bad)
 
 
-def _symm(rank, world, session, address, q, fabric, handle_type, probe_fails=False):
+def _symm(rank, world, session, q, address, fabric, handle_type, probe_fails=False):
     from mnnvl_sharp_b200 import _native as N
     from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
 

@@ -7,42 +7,22 @@ is everything the kernels do not do: argument plumbing of `ops.all_reduce*` (off
 scales, layouts, automatic backend choice), zero-copy tensor views, the data-parallel gradient
 averager and the tensor-parallel layers' sharding, quantisation and result layout.
 """
-import multiprocessing as mp
-import os
-import time
-
 import numpy as np
 import pytest
 
-CTX = mp.get_context("spawn")
+from _procs import run_processes
 
 
 def run_ranks(target, world, *args, timeout=120):
-    session = f"py{os.getpid()}_{time.monotonic_ns()}"
-    q = CTX.Queue()
-    procs = [CTX.Process(target=_entry, args=(target, r, world, session, q) + args) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = {}
-    deadline = time.time() + timeout
-    while len(results) < world and time.time() < deadline:
-        try:
-            rank, value = q.get(timeout=0.5)
-            results[rank] = value
-        except Exception:
-            if all(not p.is_alive() for p in procs) and q.empty():
-                break
-    for p in procs:
-        p.join(timeout=10)
-        if p.is_alive():
-            p.kill()
+    """target(comm, boot, *args) on every rank of a communicator on the driver stand-in."""
+    results = run_processes(_entry, world, (target,) + args, timeout, prefix="py")
     assert sorted(results) == list(range(world)), results
     for value in results.values():
         assert not isinstance(value, str), value
     return results
 
 
-def _entry(target, rank, world, session, q, *args):
+def _entry(rank, world, session, q, target, *args):
     import traceback
 
     from mnnvl_sharp_b200 import _native as N
