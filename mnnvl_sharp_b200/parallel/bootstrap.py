@@ -10,7 +10,6 @@ Every call is collective, has a deadline, and raises `NativeError` naming the ra
 from __future__ import annotations
 
 import ctypes
-import os
 
 import numpy as np
 

@@ -9,7 +9,6 @@ test of src/main.cc:152-179.
 from __future__ import annotations
 
 import ctypes
-import json
 from dataclasses import dataclass
 
 import numpy as np
