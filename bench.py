@@ -278,6 +278,8 @@ def run_ours(args) -> int:
 def main() -> int:
     args = parse_args()
     if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return 0  # launched once per GPU: one line for the job, from rank 0
         print(json.dumps({
             "impl": "reference",
             "unavailable": "reference is a CMake+MPI+yaml-cpp binary needing CUDA 13.1 (none in this image); "
