@@ -28,6 +28,17 @@ def test_reference_arm_prints_one_unavailable_line_and_exits_zero():
     assert line["impl"] == "reference" and "CUDA 13.1" in line["unavailable"]
 
 
+def test_reference_arm_under_a_per_gpu_launcher_prints_once_per_job():
+    outputs = []
+    for rank in range(3):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="3", LOCAL_RANK=str(rank))
+        done = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "3"],
+                              capture_output=True, text=True, timeout=120, env=env)
+        assert done.returncode == 0
+        outputs.append([line for line in done.stdout.splitlines() if line.strip()])
+    assert [len(o) for o in outputs] == [1, 0, 0]
+
+
 def test_bus_bandwidth_and_roofline_arithmetic():
     bench = load_bench()
     gib = 1 << 30
