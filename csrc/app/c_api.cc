@@ -292,6 +292,28 @@ void* msharp_bootstrap_connect_address(int rank, int world, const char* session,
   }
 }
 
+void* msharp_bootstrap_reform(const char* session, const char* address, int old_rank, int old_world, int hub_old_rank,
+                              int census_ms, int timeout_ms, int* new_rank, int* new_world) {
+  try {
+    msharp::BootstrapOptions opt;
+    opt.session = session != nullptr ? session : "default";
+    opt.address = address != nullptr ? address : "";
+    opt.timeout_ms = timeout_ms;
+    std::unique_ptr<msharp::Bootstrap> b = msharp::Bootstrap::reform(opt, old_rank, old_world, hub_old_rank, census_ms);
+    if (new_rank != nullptr) {
+      *new_rank = b->rank();
+    }
+    if (new_world != nullptr) {
+      *new_world = b->world();
+    }
+    g_error.clear();
+    return b.release();
+  } catch (const std::exception& ex) {
+    g_error = ex.what();
+    return nullptr;
+  }
+}
+
 void msharp_bootstrap_destroy(void* b) { delete static_cast<msharp::Bootstrap*>(b); }
 
 const char* msharp_bootstrap_env_options(void) {

@@ -22,7 +22,7 @@ using Clock = std::chrono::steady_clock;
 
 constexpr uint32_t kMagic = 0x4d534850u;  // "MSHP"
 
-enum Op : uint32_t { kHello = 1, kBarrier, kAllgather, kBroadcast, kFdGather, kFdBroadcast, kAbort };
+enum Op : uint32_t { kHello = 1, kBarrier, kAllgather, kBroadcast, kFdGather, kFdBroadcast, kAbort, kCensus };
 
 struct Header {
   uint32_t magic = kMagic;
@@ -48,6 +48,8 @@ const char* op_name(uint32_t op) {
       return "broadcast_fd";
     case kAbort:
       return "abort";
+    case kCensus:
+      return "census";
   }
   return "unknown";
 }
@@ -281,12 +283,18 @@ class HubBootstrap final : public Bootstrap {
  public:
   explicit HubBootstrap(const BootstrapOptions& opt)
       : opt_(opt), tcp_(!opt.address.empty()), tag_(session_tag(opt.session)) {
-    if (opt.rank < 0 || opt.rank >= opt.world) {
+    if (opt.census_ms <= 0 && (opt.rank < 0 || opt.rank >= opt.world)) {
       throw BootstrapError("bootstrap: rank " + std::to_string(opt.rank) + " is outside world size " +
                            std::to_string(opt.world));
     }
     try {
-      if (opt.rank == 0) {
+      if (opt.census_ms > 0) {
+        if (opt.census_hub) {
+          take_census();
+        } else {
+          join_census();
+        }
+      } else if (opt.rank == 0) {
         listen_and_accept();
       } else {
         connect_to_hub();
@@ -641,6 +649,90 @@ class HubBootstrap final : public Bootstrap {
     }
   }
 
+  // ---- re-forming after a failure (Bootstrap::reform) -------------------------------------------
+  // Hub: accept whoever shows up within the census window (opt_.world = the old world size is the
+  // most that can come), then give out dense ranks in the order of the old ranks and let go.
+  void take_census() {
+    listener_ = open_listener();
+    if (::listen(listener_, opt_.world + 8) != 0) {
+      throw BootstrapError(std::string("bootstrap: listen failed: ") + std::strerror(errno));
+    }
+    std::vector<std::pair<int, int>> joined;  // (old rank, socket)
+    const Deadline window(opt_.census_ms);
+    while (static_cast<int>(joined.size()) + 1 < opt_.world && wait_fd(listener_, POLLIN, window)) {
+      const int fd = ::accept4(listener_, nullptr, nullptr, SOCK_CLOEXEC);
+      if (fd < 0) {
+        continue;
+      }
+      if (tcp_) {
+        set_no_delay(fd);
+      }
+      Header h;
+      const Deadline hello_deadline(std::min(opt_.timeout_ms, 2000));
+      bool duplicate = false;
+      const bool readable = read_exact(fd, &h, sizeof(h), hello_deadline) == IoStatus::kOk;
+      for (const auto& member : joined) {
+        duplicate = duplicate || (readable && member.first == h.rank);
+      }
+      if (!readable || h.magic != kMagic || h.op != kCensus || h.seq != tag_ || h.rank < 0 || h.rank >= opt_.world ||
+          h.rank == opt_.old_rank || duplicate) {
+        ::close(fd);
+        continue;
+      }
+      joined.emplace_back(h.rank, fd);
+    }
+    std::sort(joined.begin(), joined.end());
+    const int new_world = static_cast<int>(joined.size()) + 1;
+    peers_.assign(static_cast<std::size_t>(new_world), -1);
+    for (std::size_t i = 0; i < joined.size(); ++i) {
+      peers_[i + 1] = joined[i].second;
+    }
+    opt_.rank = 0;
+    opt_.world = new_world;
+    const Deadline go(opt_.timeout_ms);
+    for (int r = 1; r < new_world; ++r) {
+      Header h;
+      h.op = kCensus;
+      h.seq = tag_;
+      h.rank = r;
+      h.bytes = static_cast<uint64_t>(new_world);
+      guard(write_exact(peers_[static_cast<std::size_t>(r)], &h, sizeof(h), go), r, kCensus);
+    }
+  }
+
+  void join_census() {
+    const Deadline deadline(opt_.timeout_ms + opt_.census_ms);
+    for (;;) {
+      hub_ = try_connect();
+      if (hub_ >= 0) {
+        break;
+      }
+      if (deadline.expired()) {
+        throw BootstrapError("bootstrap: old rank " + std::to_string(opt_.old_rank) +
+                             ": nobody is taking the census of session '" + opt_.session + "'");
+      }
+      std::this_thread::sleep_for(std::chrono::milliseconds(tcp_ ? 50 : 10));
+    }
+    Header h;
+    h.op = kCensus;
+    h.seq = tag_;
+    h.rank = opt_.old_rank;
+    h.bytes = 0;
+    if (write_exact(hub_, &h, sizeof(h), deadline) != IoStatus::kOk) {
+      throw BootstrapError("bootstrap: old rank " + std::to_string(opt_.old_rank) + ": the census was closed before this rank joined");
+    }
+    Header answer;
+    const IoStatus st = read_exact(hub_, &answer, sizeof(answer), deadline);
+    if (st != IoStatus::kOk || answer.magic != kMagic || answer.op != kCensus || answer.seq != tag_ || answer.rank <= 0 ||
+        answer.bytes > 1u << 20 || static_cast<uint64_t>(answer.rank) >= answer.bytes) {
+      throw BootstrapError("bootstrap: old rank " + std::to_string(opt_.old_rank) +
+                           (st == IoStatus::kTimeout ? ": no answer from the census in time"
+                                                     : ": the census was closed before this rank joined"));
+    }
+    opt_.rank = answer.rank;
+    opt_.world = static_cast<int>(answer.bytes);
+  }
+
   void abort_peers_after_failed_join() noexcept {
     const Deadline deadline(200);
     Header h;
@@ -774,6 +866,23 @@ std::unique_ptr<Bootstrap> Bootstrap::connect(const BootstrapOptions& options) {
     return std::make_unique<SoloBootstrap>();
   }
   return std::make_unique<HubBootstrap>(options);
+}
+
+std::unique_ptr<Bootstrap> Bootstrap::reform(const BootstrapOptions& options, int old_rank, int old_world,
+                                             int hub_old_rank, int census_ms) {
+  if (old_world <= 0 || old_rank < 0 || old_rank >= old_world || hub_old_rank < 0 || hub_old_rank >= old_world) {
+    throw BootstrapError("bootstrap: reform needs 0 <= old_rank, hub_old_rank < old_world");
+  }
+  if (census_ms <= 0) {
+    throw BootstrapError("bootstrap: reform needs a positive census time");
+  }
+  BootstrapOptions opt = options;
+  opt.rank = 0;
+  opt.world = old_world;
+  opt.old_rank = old_rank;
+  opt.census_ms = census_ms;
+  opt.census_hub = old_rank == hub_old_rank;
+  return std::make_unique<HubBootstrap>(opt);
 }
 
 namespace {

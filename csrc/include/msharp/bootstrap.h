@@ -36,6 +36,10 @@ struct BootstrapOptions {
   // all interfaces and every other rank connects to host:port; the session name is checked in
   // the greeting so that two jobs that were given the same port by mistake do not mix.
   std::string address;
+  // Set by Bootstrap::reform only (see there).
+  int census_ms = 0;
+  int old_rank = -1;
+  bool census_hub = false;
 };
 
 class Bootstrap {
@@ -67,6 +71,18 @@ class Bootstrap {
   int broadcast_int(int value, int root);
 
   static std::unique_ptr<Bootstrap> connect(const BootstrapOptions& options);
+
+  // Re-form the control plane among the ranks that are still there after a failure. The survivors
+  // of a job of `old_world` ranks call this with a NEW session name that they all derive the same
+  // way (for instance the old name plus a generation number). The survivor whose old rank is
+  // `hub_old_rank` (0 unless rank 0 is the one that was lost: the error that reported the failure
+  // names the lost rank) takes a census for `census_ms` milliseconds, or until all `old_world`
+  // ranks have shown up; whoever joined in time gets a new dense rank (the hub 0, the others in the
+  // order of their old ranks) and the new world size, readable from rank() / world() of the result.
+  // A rank that arrives after the census closed gets a BootstrapError. The reference has no
+  // counterpart: a lost rank ends its job (src/main.cc:496-502).
+  static std::unique_ptr<Bootstrap> reform(const BootstrapOptions& options, int old_rank, int old_world,
+                                           int hub_old_rank, int census_ms);
   // Options from rank_from_env() / MSHARP_SESSION (or MASTER_PORT, or the Slurm / Open MPI job id) / MSHARP_HUB_ADDR
   // (host:port, selects TCP) / MSHARP_BOOTSTRAP_TIMEOUT_MS in the environment.
   static BootstrapOptions options_from_env();

@@ -48,6 +48,10 @@ const char* msharp_run_cpu_only(int argc, const char* const* argv);
 void* msharp_bootstrap_connect(int rank, int world, const char* session, int timeout_ms);
 // address: NULL or "" for Unix-domain sockets on one host, "host:port" for TCP across hosts.
 void* msharp_bootstrap_connect_address(int rank, int world, const char* session, const char* address, int timeout_ms);
+// Re-form the control plane among the survivors of a job (see Bootstrap::reform). Returns the new
+// handle and, through new_rank / new_world, this process's place in it.
+void* msharp_bootstrap_reform(const char* session, const char* address, int old_rank, int old_world, int hub_old_rank,
+                              int census_ms, int timeout_ms, int* new_rank, int* new_world);
 int msharp_bootstrap_can_pass_fds(void* bootstrap);
 // JSON: rank, world, session, address, timeout_ms, launched_by, as read from the environment.
 const char* msharp_bootstrap_env_options(void);

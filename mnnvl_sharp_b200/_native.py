@@ -52,6 +52,7 @@ _SIGNATURES = {
     "msharp_run_cpu_only": (c_char_p, [c_int, POINTER(c_char_p)]),
     "msharp_bootstrap_connect": (c_void_p, [c_int, c_int, c_char_p, c_int]),
     "msharp_bootstrap_connect_address": (c_void_p, [c_int, c_int, c_char_p, c_char_p, c_int]),
+    "msharp_bootstrap_reform": (c_void_p, [c_char_p, c_char_p, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     "msharp_bootstrap_can_pass_fds": (c_int, [c_void_p]),
     "msharp_bootstrap_env_options": (c_char_p, []),
     "msharp_bootstrap_destroy": (None, [c_void_p]),

@@ -51,6 +51,29 @@ class Bootstrap:
         dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
         return cls(rank, world, "pg" + box[0], timeout_ms, address)
 
+    @classmethod
+    def reform(cls, session: str, old_rank: int, old_world: int, hub_old_rank: int = 0, census_ms: int = 2000,
+               timeout_ms: int = 30000, address: str | None = None) -> "Bootstrap":
+        """Re-form the control plane among the ranks that are left after a failure.
+
+        Every survivor calls this with the same NEW session name (for instance the old one plus a
+        generation number) and its old rank. The survivor with old rank `hub_old_rank` takes a census
+        for `census_ms` milliseconds (or until all `old_world` ranks have joined); those who joined get
+        dense new ranks (the hub 0, then by old rank) and the new world size, available as `.rank` /
+        `.world` of the result. Communicators and symmetric buffers of the old job are not carried
+        over: build new ones on the new control plane (the old ones refer to the lost rank's memory)."""
+        self = cls.__new__(cls)
+        new_rank = ctypes.c_int(-1)
+        new_world = ctypes.c_int(0)
+        self.session = session
+        self.address = address or ""
+        self._h = N.pointer(N.lib.msharp_bootstrap_reform(session.encode(), self.address.encode(), old_rank, old_world,
+                                                          hub_old_rank, census_ms, timeout_ms, ctypes.byref(new_rank),
+                                                          ctypes.byref(new_world)))
+        self.rank = new_rank.value
+        self.world = new_world.value
+        return self
+
     @property
     def can_pass_fds(self) -> bool:
         return bool(N.lib.msharp_bootstrap_can_pass_fds(self._h))

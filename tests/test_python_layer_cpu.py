@@ -292,3 +292,87 @@ def test_tensor_parallel_layers_match_the_sum_of_partial_products(world):
     for linear_err, same, quant_err, ffn_err, shape, dtype in run_ranks(_tensor_parallel_layers, world, timeout=300).values():
         assert linear_err < 2 ** -7 and ffn_err < 2 ** -7  # BF16 rounding of the result only
         assert same and quant_err < 0.08 and shape == (128, 128) and dtype == "torch.float32"
+
+
+# ------------------------------------------------------------------------------------ shrinking after a failure
+def _lose_a_rank_and_go_on(rank, world, session, q, lost, address, address_after):
+    """`lost` leaves between steps. The others notice at their next host-side agreement, re-form the
+    control plane among themselves, build a new communicator and buffer, and carry on all-reducing."""
+    import os
+    import traceback
+
+    import torch
+
+    from mnnvl_sharp_b200 import _native as N
+    from mnnvl_sharp_b200 import ops
+    from mnnvl_sharp_b200.parallel import Bootstrap, Communicator
+
+    try:
+        N.lib.msharp_fake_driver_reset(8)
+        N.lib.msharp_fake_driver_set_attribute(128, 1 if address else 0)  # fabric handles when over TCP
+        boot = Bootstrap(rank, world, session, timeout_ms=5000, address=address)
+        comm = Communicator(boot, rank % 8, fake_driver=True)
+        buf = comm.alloc(4096)
+        x = buf.tensor(torch.float16)
+        steps = 0
+        error = ""
+        try:
+            for step in range(4):
+                if rank == lost and step == 2:
+                    os._exit(0)  # between steps, nothing in flight
+                boot.barrier()  # agreement before every step: a missing rank shows up here
+                x.fill_(float(rank + 1))
+                ops.all_reduce_pull(comm, buf, "f16")
+                assert float(x[0]) == world * (world + 1) / 2
+                steps += 1
+        except N.NativeError as ex:
+            error = str(ex)
+        # the old communicator refers to the lost rank's memory: drop it without collective teardown
+        del x
+        hub = 0 if lost != 0 else 1  # the error names the lost rank; everybody derives the same hub from it
+        again = Bootstrap.reform(session + ".g1", old_rank=rank, old_world=world, hub_old_rank=hub, census_ms=1500,
+                                 timeout_ms=10000, address=address_after or None)
+        comm2 = Communicator(again, again.rank % 8, fake_driver=True)
+        buf2 = comm2.alloc(4096)
+        y = buf2.tensor(torch.float16)
+        y.fill_(float(rank + 1))  # old rank numbers as values: the sum says who is still there
+        again.barrier()
+        ops.all_reduce_pull(comm2, buf2, "f16")
+        total = float(y[0])
+        del y
+        again.barrier()
+        buf2.free()
+        comm2.close()
+        again.close()
+        q.put((rank, dict(steps=steps, error=error, new_rank=again.rank, new_world=again.world, total=total)))
+    except Exception:  # noqa: BLE001
+        q.put((rank, traceback.format_exc()))
+    q.close()
+    q.join_thread()  # the result is on its way before the process ends
+    os._exit(0)  # skip the old control plane's teardown: its peer is gone
+
+
+@pytest.mark.parametrize("lost,tcp", [(2, False), (1, False), (0, False), (3, True)])
+def test_survivors_reform_the_job_and_carry_on(lost, tcp):
+    import socket
+
+    world = 4
+    address = address_after = ""
+    if tcp:
+        with socket.socket() as a, socket.socket() as b:
+            a.bind(("127.0.0.1", 0))
+            b.bind(("127.0.0.1", 0))
+            address, address_after = f"127.0.0.1:{a.getsockname()[1]}", f"127.0.0.1:{b.getsockname()[1]}"
+    results = run_processes(_lose_a_rank_and_go_on, world, (lost, address, address_after), timeout=90, prefix="el")
+    survivors = [r for r in range(world) if r != lost]
+    assert sorted(results) == survivors, results
+    for value in results.values():
+        assert not isinstance(value, str), value
+    expected_total = float(sum(r + 1 for r in survivors))
+    hub = 0 if lost != 0 else 1
+    order = [hub] + [r for r in survivors if r != hub]
+    for r in survivors:
+        v = results[r]
+        assert v["steps"] == 2 and v["error"], v          # two good steps, then the loss was noticed on the host
+        assert v["new_world"] == 3 and v["new_rank"] == order.index(r), v
+        assert v["total"] == expected_total
