@@ -130,26 +130,40 @@ def build_native(verbose: bool = False) -> dict[str, Path]:
     return result
 
 
-def build_sanitized_tests(verbose: bool = False) -> Path:
-    """The C++ unit-test runner with AddressSanitizer and UndefinedBehaviorSanitizer on all host
-    code (device objects are linked as built). Used by `tests/test_native_cpp.py`."""
+def build_sanitized_tests(verbose: bool = False, sanitizer: str = "address,undefined") -> Path:
+    """The C++ unit-test runner with sanitizers on all host code (device objects are linked as
+    built): "address,undefined" (AddressSanitizer + UndefinedBehaviorSanitizer) or "thread"
+    (ThreadSanitizer; the runner has tests whose ranks are threads). Used by `tests/test_native_cpp.py`."""
+    if sanitizer not in ("address,undefined", "thread"):
+        raise ValueError("sanitizer must be 'address,undefined' or 'thread'")
     build_native(verbose)
-    san = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined"]
+    tag = "san" if sanitizer != "thread" else "tsan"
+    san = [f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer"]
+    if sanitizer != "thread":
+        san.append("-fno-sanitize-recover=undefined")
     sources = [s for s in LIB_SOURCES + [s for s in OPTIONAL_LIB_SOURCES if (CSRC / s).exists()]]
     hm = _headers_mtime()
     objs = []
+    stale = []
     for rel in sources + ["tests/test_main.cc"]:
         if rel.endswith(".cu"):
             objs.append(str(OBJ / (rel.replace("/", "_") + ".o")))
             continue
         src = CSRC / rel
-        obj = OBJ / ("san_" + rel.replace("/", "_") + ".o")
+        obj = OBJ / (f"{tag}_" + rel.replace("/", "_") + ".o")
         if not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hm):
-            if verbose:
-                print("  cc (sanitized)", rel, flush=True)
-            _run(["g++", *CXX_FLAGS, *san, *INCLUDES, "-DMSHARP_HAS_BULK_MULTIMEM=0", "-c", str(src), "-o", str(obj)])
+            stale.append((rel, src, obj))
         objs.append(str(obj))
-    exe = OUT / "msharp_cpp_tests_san"
+
+    def compile_one(item):
+        rel, src, obj = item
+        if verbose:
+            print(f"  cc ({sanitizer})", rel, flush=True)
+        _run(["g++", *CXX_FLAGS, *san, *INCLUDES, "-DMSHARP_HAS_BULK_MULTIMEM=0", "-c", str(src), "-o", str(obj)])
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        list(pool.map(compile_one, stale))
+    exe = OUT / f"msharp_cpp_tests_{tag}"
     _run(["g++", *san, "-o", str(exe), *objs, "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-ldl", "-lrt", "-lpthread"])
     return exe
 

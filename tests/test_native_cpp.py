@@ -19,6 +19,16 @@ def test_native_cpp_suite_under_address_and_ub_sanitizers():
     assert "all native tests passed" in proc.stdout
 
 
+def test_native_cpp_suite_under_thread_sanitizer():
+    """The runner's multi-threaded tests (ranks as threads over TCP and Unix sockets, the shared
+    state of the driver stand-in) with data-race detection on all host code."""
+    exe = _build.build_sanitized_tests(sanitizer="thread")
+    proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600,
+                          env={"TSAN_OPTIONS": "halt_on_error=1:second_deadlock_stack=1"})
+    assert proc.returncode == 0, (proc.stdout + proc.stderr)[-4000:]
+    assert "all native tests passed" in proc.stdout and "ThreadSanitizer" not in proc.stderr
+
+
 def test_cmake_build_and_ctest(tmp_path):
     """The CMake route builds the same library, binary and tests for sm_100a and its ctest passes."""
     import os
