@@ -66,6 +66,7 @@ struct RankRun {
   LaunchShape shape;
   std::string kernel_variant;
   std::string bulk_variant;
+  std::vector<double> local_device_ms;  // this rank's own device time of every measured iteration
 
   void* input_ptr() const { return reinterpret_cast<void*>(mem->input_ptr(rank.world_rank)); }
   void* output_ptr() const { return reinterpret_cast<void*>(mem->output_ptr(rank.world_rank)); }
@@ -222,6 +223,7 @@ void run_iteration(RankRun& run, bool measure, double* device_ms, double* wall_m
     emulate_collective(run);
     const double local = ms_since(t0);
     if (measure) {
+      run.local_device_ms.push_back(local);
       *device_ms = run.comm.reduce_max(local);
       *wall_ms = *device_ms;
     }
@@ -241,6 +243,7 @@ void run_iteration(RankRun& run, bool measure, double* device_ms, double* wall_m
   if (measure) {
     float local_ms = 0.0f;
     MSHARP_CUDA(cudaEventElapsedTime(&local_ms, run.start, run.stop));
+    run.local_device_ms.push_back(static_cast<double>(local_ms));
     *device_ms = run.comm.reduce_max(static_cast<double>(local_ms));
     *wall_ms = run.comm.reduce_max(local_wall);
   }
@@ -365,6 +368,7 @@ void measure(RankRun& run, RunReport& report) {
     report.phase_exit_barrier_us = run.comm.allgather_double(p.exit_barrier_us);
   }
   report.hashes = run.comm.allgather_u64(replica_hash(run));
+  report.device_ms_median_by_rank = run.comm.allgather_double(summarize(run.local_device_ms).median);
   report.has_results = true;
   report.device_ms = summarize(device_times);
   report.wall_ms = summarize(wall_times);

@@ -153,6 +153,27 @@ std::string json_report(const RunReport& r) {
     w.key("tolerance_ulp").value(r.tolerance_ulp);
     w.key("tolerance_abs").value(r.tolerance_abs);
     w.key("within_tolerance").value(r.within_tolerance);
+    if (!r.device_ms_median_by_rank.empty()) {
+      w.key("sharp_kernel_ms_median_by_rank").begin_array();
+      for (double v : r.device_ms_median_by_rank) {
+        w.value(v);
+      }
+      w.end_array();
+    }
+    if (n > 1 && r.device_ms.median > 0.0) {
+      // Bytes that must cross this GPU's NVLink port in one direction, at the 770 GB/s that a peer copy
+      // reaches on this hardware: in-switch pull S(1 + 1/N), peer-load path 2S(N-1)/N, push (N-1)S.
+      const double s_bytes = static_cast<double>(r.cfg.bytes);
+      double link_bytes = s_bytes * (1.0 + 1.0 / n);
+      if (r.cfg.sharp_backend == Backend::kSwF32) {
+        link_bytes = 2.0 * s_bytes * (n - 1) / n;
+      } else if (r.cfg.sharp_backend == Backend::kTmaAsync) {
+        link_bytes = s_bytes * (n - 1);
+      }
+      const double bound_ms = link_bytes / 770e6;
+      w.key("link_bound_ms").value(bound_ms);
+      w.key("link_bound_fraction").value(bound_ms / r.device_ms.median);
+    }
     w.key("algbw_gb_s").value(algbw_gb_s(r.cfg.bytes, r.device_ms.median));
     w.key("busbw_gb_s").value(busbw_gb_s(r.cfg.bytes, r.device_ms.median, n));
     w.key("effective_logical_bandwidth_gib_s_median").value(logical_gib_s(r.cfg.bytes, r.device_ms.median, n));

@@ -45,6 +45,7 @@ struct RunReport {
   int grid = 0;
   int block = 0;
   double control_init_ms = 0.0;
+  std::vector<double> device_ms_median_by_rank;  // every rank's own median kernel time (the headline is the max per iteration)
   // with --trace-phases: per rank, microseconds of the last measured iteration as CTA 0 saw them
   std::vector<double> phase_entry_barrier_us, phase_transfer_us, phase_exit_barrier_us;
 };

@@ -47,6 +47,8 @@ def test_full_run_reports_matching_replicas_and_exit_code_zero(flags):
     assert r["kernel_variant"] == "host_emulation_f32_sum" and r["handle_type"] == "posix_fd"
     assert r["sharp_kernel_ms"]["max"] >= r["sharp_kernel_ms"]["min"] > 0
     assert len(r["host_mapping"]) == 4 and len(r["peer_init_local_ms_by_rank"]) == 4
+    assert len(r["sharp_kernel_ms_median_by_rank"]) == 4 and max(r["sharp_kernel_ms_median_by_rank"]) <= r["sharp_kernel_ms"]["max"]
+    assert r["link_bound_ms"] > 0 and r["link_bound_fraction"] == pytest.approx(r["link_bound_ms"] / r["sharp_kernel_ms"]["median"], rel=1e-3)
 
 
 def test_a_corrupted_replica_gives_exit_code_two_on_the_whole_job():
